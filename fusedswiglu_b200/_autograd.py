@@ -1,0 +1,60 @@
+"""Shared forward/backward of the two autograd Functions.
+
+Mirrors the data flow of the reference's ``FusedSwiGLU`` (fused_swiglu/swiglu.py:16-58):
+forward saves ``(x, w_gate, w_up, x@w_gate, x@w_up)`` and returns only ``out``;
+backward runs the gate-gradient step, the input-gradient GEMM and the
+weight-gradient GEMM and returns ``(dX, dW_gate, dW_up)``.
+
+Differences, all on the accurate side of the reference's tolerances:
+  * dX is ONE GEMM accumulating both products in fp32 (the reference rounds each
+    product to 16 bits and adds, swiglu.py:45);
+  * dW is reduced over all bs*sq tokens in one launch with a single rounding (the
+    reference rounds per batch and sums in 16 bits, swiglu.py:51-57), and is
+    returned as (d_model, d_intermediate) - autograd reduces the reference's
+    (1, d_model, d_intermediate) to that shape anyway;
+  * gradients that autograd does not need are not computed.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _launch
+
+
+def swiglu_forward(ctx, x, w_gate, w_up, *, fast_accum: bool):
+    assert (
+        x.shape[2] == w_up.shape[0]
+    ), f"Dimension mismatch. Expected a.shape[2] ({x.shape[2]}) to be equal to b.shape[0] ({w_up.shape[0]})"
+    assert w_up.shape == w_gate.shape, "Expected both weight matrices to have same shape"
+    assert x.ndim == 3 and w_up.ndim == 2, "Incorrect number of dimensions for LHS or RHS"
+    assert x.dtype == w_gate.dtype == w_up.dtype, "Expected input and weights of one dtype"
+    bs, sq, dm = x.shape
+    di = w_up.shape[1]
+    x2d = x.contiguous().view(bs * sq, dm)
+    wg = w_gate.contiguous()
+    wu = w_up.contiguous()
+    need_grad = torch.is_grad_enabled() and (x.requires_grad or w_gate.requires_grad or w_up.requires_grad)
+    out, g, u = _launch.forward(x2d, wg, wu, fast_accum=fast_accum, save_activations=need_grad)
+    if need_grad:
+        ctx.save_for_backward(x2d, wg, wu, g, u)
+    ctx.in_shape = (bs, sq, dm)
+    return out.view(bs, sq, di)
+
+
+def swiglu_backward(ctx, grad_output, *, fast_accum: bool):
+    x2d, wg, wu, g, u = ctx.saved_tensors
+    bs, sq, dm = ctx.in_shape
+    di = wg.shape[1]
+    need_x, need_g, need_u = ctx.needs_input_grad[:3]
+    dout = grad_output.contiguous().view(bs * sq, di)
+    if dout.dtype != x2d.dtype:
+        dout = dout.to(x2d.dtype)
+    dg, du = _launch.gate_grad(dout, g, u)
+    dx = dwg = dwu = None
+    if need_x:
+        dx = _launch.grad_input(dg, du, wg, wu).view(bs, sq, dm)
+    if need_g or need_u:
+        dwg, dwu = _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum)
+        dwg = dwg if need_g else None
+        dwu = dwu if need_u else None
+    return dx, dwg, dwu

@@ -1,0 +1,112 @@
+"""Host launchers: torch tensors in, C-ABI calls out.
+
+torch is used only for device memory, the current stream and dtype bookkeeping;
+every arithmetic result comes from libfused_swiglu_sm100.so.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_DTYPE_CODE = {torch.bfloat16: _lib.FSW_BF16, torch.float16: _lib.FSW_FP16}
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise AssertionError(f"Expected torch.bfloat16 or torch.float16 tensors, got {t.dtype}") from None
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError(
+                "fused_swiglu runs on CUDA tensors only (sm_100a); there is no CPU path"
+            )
+        if t.device != dev:
+            raise RuntimeError(f"all tensors must be on one device, got {dev} and {t.device}")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def forward(
+    x2d: torch.Tensor,
+    w_gate: torch.Tensor,
+    w_up: torch.Tensor,
+    *,
+    fast_accum: bool = False,
+    save_activations: bool = True,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """out, g, u for x2d (T, dm) and weights (dm, di); g and u are None when not saved."""
+    _require_cuda(x2d, w_gate, w_up)
+    T, dm = x2d.shape
+    di = w_gate.shape[1]
+    out = torch.empty((T, di), device=x2d.device, dtype=x2d.dtype)
+    g = torch.empty_like(out) if save_activations else None
+    u = torch.empty_like(out) if save_activations else None
+    with torch.cuda.device(x2d.device):
+        rc = _lib.load().fsw_forward(
+            x2d.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), out.data_ptr(),
+            g.data_ptr() if g is not None else None,
+            u.data_ptr() if u is not None else None,
+            T, dm, di, _code(x2d),
+            _lib.FSW_ACC_F16 if fast_accum else _lib.FSW_ACC_F32, _stream(x2d),
+        )
+    _lib.check("fsw_forward", rc)
+    return out, g, u
+
+
+def gate_grad(dout: torch.Tensor, g: torch.Tensor, u: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(dg, du) from contiguous dout, g, u of one shape."""
+    _require_cuda(dout, g, u)
+    dg = torch.empty_like(dout)
+    du = torch.empty_like(dout)
+    with torch.cuda.device(dout.device):
+        rc = _lib.load().fsw_backward_elementwise(
+            dout.data_ptr(), g.data_ptr(), u.data_ptr(), dg.data_ptr(), du.data_ptr(),
+            dout.numel(), _code(dout), _stream(dout),
+        )
+    _lib.check("fsw_backward_elementwise", rc)
+    return dg, du
+
+
+def grad_input(dg: torch.Tensor, du: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """dX (T, dm) = dg @ w_gate^T + du @ w_up^T, accumulated in fp32 in one GEMM."""
+    _require_cuda(dg, du, w_gate, w_up)
+    T, di = dg.shape
+    dm = w_gate.shape[0]
+    dx = torch.empty((T, dm), device=dg.device, dtype=dg.dtype)
+    with torch.cuda.device(dg.device):
+        rc = _lib.load().fsw_backward_dx(
+            dg.data_ptr(), du.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), dx.data_ptr(),
+            T, dm, di, _code(dg), _lib.FSW_ACC_F32, _stream(dg),
+        )
+    _lib.check("fsw_backward_dx", rc)
+    return dx
+
+
+def grad_weights(
+    x2d: torch.Tensor, dg: torch.Tensor, du: torch.Tensor, *, fast_accum: bool = False,
+    out_gate: Optional[torch.Tensor] = None, out_up: Optional[torch.Tensor] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(dW_gate, dW_up), each (dm, di), reduced over all T rows of x2d."""
+    _require_cuda(x2d, dg, du)
+    T, dm = x2d.shape
+    di = dg.shape[1]
+    dwg = out_gate if out_gate is not None else torch.empty((dm, di), device=x2d.device, dtype=x2d.dtype)
+    dwu = out_up if out_up is not None else torch.empty((dm, di), device=x2d.device, dtype=x2d.dtype)
+    with torch.cuda.device(x2d.device):
+        rc = _lib.load().fsw_backward_dw(
+            x2d.data_ptr(), dg.data_ptr(), du.data_ptr(), dwg.data_ptr(), dwu.data_ptr(),
+            T, dm, di, _code(x2d),
+            _lib.FSW_ACC_F16 if fast_accum else _lib.FSW_ACC_F32, _stream(x2d),
+        )
+    _lib.check("fsw_backward_dw", rc)
+    return dwg, dwu

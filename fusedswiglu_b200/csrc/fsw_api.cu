@@ -1,0 +1,568 @@
+// C ABI of libfused_swiglu_sm100.so (declared in include/fused_swiglu.h):
+// argument checking, TMA tensor-map construction, UMMA descriptor constants and
+// kernel launches.  No device memory is allocated here; the only per-device
+// state is a cache of device attributes.
+#include "../../include/fused_swiglu.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "fsw_gemm.cuh"
+
+namespace fsw {
+
+// ------------------------------------------------------------------ errors --
+static thread_local char t_err[512] = "";
+
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_err, sizeof(t_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define FSW_CUDA(call)                                                                   \
+  do {                                                                                   \
+    cudaError_t e_ = (call);                                                             \
+    if (e_ != cudaSuccess)                                                               \
+      return fail(FSW_ECUDA, "%s failed: %s", #call, cudaGetErrorString(e_));            \
+  } while (0)
+
+// ----------------------------------------------------------------- options --
+struct Options {
+  int64_t cta_group = 2;
+  int64_t group_m = 16;
+  // Debug overrides of the UMMA shared-memory descriptor fields (0 = built-in).
+  int64_t k_lbo = 0, k_sbo = 0, k_kadv = 0;
+  int64_t mn_lbo = 0, mn_sbo = 0, mn_kadv = 0;
+};
+static Options g_opt;
+
+// Status word the kernels write when a bounded wait gives up.
+__device__ uint32_t g_status_word;
+
+// ------------------------------------------------------------ device cache --
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+  bool ready = false;
+  int sm_count = 0, cc_major = 0, cc_minor = 0;
+  int64_t smem_optin = 0;
+  int max_pairs = 0;  // co-resident 2-CTA clusters of the GEMM kernels
+  uint32_t* status = nullptr;
+};
+static DeviceInfo g_dev[kMaxDevices];
+static std::mutex g_mu;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+template <int MODE, int CG, typename T, bool ACC16>
+static cudaError_t prepare_kernel() {
+  return cudaFuncSetAttribute(gemm_kernel<MODE, CG, T, ACC16>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              TileCfg<MODE, CG>::SMEM_BYTES);
+}
+
+template <int MODE, int CG>
+static cudaError_t prepare_mode() {
+  cudaError_t e;
+  if ((e = prepare_kernel<MODE, CG, __nv_bfloat16, false>()) != cudaSuccess) return e;
+  if ((e = prepare_kernel<MODE, CG, __half, false>()) != cudaSuccess) return e;
+  return prepare_kernel<MODE, CG, __half, true>();
+}
+
+static int ensure_device(DeviceInfo** out) {
+  int dev = 0;
+  FSW_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(FSW_EINVAL, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceInfo& d = g_dev[dev];
+  if (!d.ready) {
+    FSW_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    FSW_CUDA(cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev));
+    if (d.cc_major != 10)
+      return fail(FSW_EDEVICE,
+                  "device %d is compute capability %d.%d; this library runs on 10.x (B200) only",
+                  dev, d.cc_major, d.cc_minor);
+    int v = 0;
+    FSW_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    FSW_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    d.smem_optin = v;
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      FSW_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+      if (fn == nullptr || qres != cudaDriverEntryPointSuccess)
+        return fail(FSW_EUNAVAILABLE, "driver does not provide cuTensorMapEncodeTiled");
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    FSW_CUDA((prepare_mode<MODE_FWD, 1>()));
+    FSW_CUDA((prepare_mode<MODE_DX, 1>()));
+    FSW_CUDA((prepare_mode<MODE_DW, 1>()));
+    FSW_CUDA((prepare_mode<MODE_FWD, 2>()));
+    FSW_CUDA((prepare_mode<MODE_DX, 2>()));
+    FSW_CUDA((prepare_mode<MODE_DW, 2>()));
+    void* sp = nullptr;
+    FSW_CUDA(cudaGetSymbolAddress(&sp, g_status_word));
+    d.status = static_cast<uint32_t*>(sp);
+    // How many CTA pairs can be resident at once (a GPC with an odd SM count
+    // leaves one SM without a partner).
+    {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * d.sm_count, 1, 1);
+      cfg.blockDim = dim3(TileCfg<MODE_FWD, 2>::THREADS, 1, 1);
+      cfg.dynamicSmemBytes = TileCfg<MODE_FWD, 2>::SMEM_BYTES;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      cudaError_t e = cudaOccupancyMaxActiveClusters(
+          &n, gemm_kernel<MODE_FWD, 2, __nv_bfloat16, false>, &cfg);
+      if (e != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        n = d.sm_count / 2;
+      }
+      d.max_pairs = n;
+    }
+    d.ready = true;
+  }
+  *out = &d;
+  return FSW_OK;
+}
+
+// ------------------------------------------------------------- tensor maps --
+// Row-major (outer, inner) array of 16-bit elements; box = box_outer rows of 64
+// elements (128 bytes), 128-byte swizzle.
+static int make_map(CUtensorMap* m, const void* ptr, int dtype, uint64_t inner, uint64_t outer,
+                    uint32_t box_outer, const char* what) {
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {inner * 2};
+  cuuint32_t box[2] = {64, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(
+      m, dtype == FSW_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+      const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(FSW_ECUDA, "cuTensorMapEncodeTiled(%s: inner=%llu outer=%llu box_outer=%u) -> %d",
+                what, (unsigned long long)inner, (unsigned long long)outer, box_outer, (int)r);
+  return FSW_OK;
+}
+
+// UMMA instruction descriptor, kind::f16: D format [4,6), A format [7,10),
+// B format [10,13), A major bit 15, B major bit 16, N>>3 at [17,23), M>>4 at [24,29).
+static uint32_t make_idesc(int dtype, bool acc16, int a_major, int b_major, int m, int n) {
+  uint32_t d = 0;
+  d |= (acc16 ? 0u : 1u) << 4;
+  d |= (dtype == FSW_BF16 ? 1u : 0u) << 7;
+  d |= (dtype == FSW_BF16 ? 1u : 0u) << 10;
+  d |= static_cast<uint32_t>(a_major) << 15;
+  d |= static_cast<uint32_t>(b_major) << 16;
+  d |= static_cast<uint32_t>(n >> 3) << 17;
+  d |= static_cast<uint32_t>(m >> 4) << 24;
+  return d;
+}
+
+// UMMA shared-memory descriptor without the start address: leading byte offset
+// at [16,30), stride byte offset at [32,46) (both >>4), version 1 at bit 46,
+// layout type SWIZZLE_128B (2) at [61,64).
+static uint64_t make_sdesc(uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+static void fill_operand_desc(int major, uint64_t* desc, uint32_t* kadv) {
+  if (major == MAJOR_K) {
+    // rows of 64 elements = one 128-byte swizzle row; 8-row groups 1024 B apart;
+    // a K=16 step moves 32 bytes inside the swizzle row.
+    const uint32_t lbo = g_opt.k_lbo ? (uint32_t)g_opt.k_lbo : 16u;
+    const uint32_t sbo = g_opt.k_sbo ? (uint32_t)g_opt.k_sbo : 1024u;
+    *desc = make_sdesc(lbo, sbo);
+    *kadv = g_opt.k_kadv ? (uint32_t)g_opt.k_kadv : 32u;
+  } else {
+    // 64(MN) x 64(K) boxes: K rows of 128 bytes; 8-row K groups 1024 B apart
+    // (stride offset); the next 64 MN elements are one whole box (8192 B) away
+    // (leading offset); a K=16 step is 16 rows = 2048 bytes.
+    const uint32_t lbo = g_opt.mn_lbo ? (uint32_t)g_opt.mn_lbo : 8192u;
+    const uint32_t sbo = g_opt.mn_sbo ? (uint32_t)g_opt.mn_sbo : 1024u;
+    *desc = make_sdesc(lbo, sbo);
+    *kadv = g_opt.mn_kadv ? (uint32_t)g_opt.mn_kadv : 2048u;
+  }
+}
+
+// ---------------------------------------------------------------- launches --
+template <int MODE, int CG, typename T, bool ACC16>
+static cudaError_t launch_one(const GemmParams& p, int grid, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(TileCfg<MODE, CG>::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = TileCfg<MODE, CG>::SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gemm_kernel<MODE, CG, T, ACC16>, p);
+}
+
+template <int MODE, int CG>
+static cudaError_t launch_cg(const GemmParams& p, int grid, int dtype, bool acc16,
+                             cudaStream_t st) {
+  if (dtype == FSW_BF16) return launch_one<MODE, CG, __nv_bfloat16, false>(p, grid, st);
+  if (acc16) return launch_one<MODE, CG, __half, true>(p, grid, st);
+  return launch_one<MODE, CG, __half, false>(p, grid, st);
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int check_common(int64_t T, int64_t dm, int64_t di, int dtype, int accum) {
+  if (dtype != FSW_BF16 && dtype != FSW_FP16) return fail(FSW_EINVAL, "unknown dtype %d", dtype);
+  if (accum != FSW_ACC_F32 && accum != FSW_ACC_F16)
+    return fail(FSW_EINVAL, "unknown accumulate mode %d", accum);
+  if (accum == FSW_ACC_F16 && dtype != FSW_FP16)
+    return fail(FSW_EINVAL, "fp16 accumulation needs fp16 tensors");
+  if (T < 0 || dm <= 0 || di <= 0)
+    return fail(FSW_EINVAL, "bad shape T=%lld dm=%lld di=%lld", (long long)T, (long long)dm,
+                (long long)di);
+  if ((dm & 7) || (di & 7))
+    return fail(FSW_EINVAL, "d_model (%lld) and d_intermediate (%lld) must be multiples of 8",
+                (long long)dm, (long long)di);
+  if (T >= (1ll << 31) || dm >= (1ll << 31) || di >= (1ll << 31))
+    return fail(FSW_EINVAL, "extent exceeds 2^31-1");
+  return FSW_OK;
+}
+
+template <int MODE>
+static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t st,
+                    DeviceInfo* d) {
+  const int cg = (int)g_opt.cta_group;
+  const int tile_m = 128 * cg;
+  const int tile_n = (MODE == MODE_DX) ? 256 : 128;
+  p.num_m_tiles = (rows + tile_m - 1) / tile_m;
+  p.num_n_tiles = (p.N + tile_n - 1) / tile_n;
+  p.group_m = (int)g_opt.group_m < 1 ? 1 : (int)g_opt.group_m;
+  p.status = d->status;
+  const int a_major = (MODE == MODE_DW) ? MAJOR_MN : MAJOR_K;
+  const int b_major = (MODE == MODE_DX) ? MAJOR_K : MAJOR_MN;
+  fill_operand_desc(a_major, &p.a_desc, &p.a_kadv);
+  fill_operand_desc(b_major, &p.b_desc, &p.b_kadv);
+  p.idesc = make_idesc(dtype, acc16, a_major, b_major, 128 * cg, 256);
+  const long long tiles = (long long)p.num_m_tiles * p.num_n_tiles;
+  if (tiles <= 0) return FSW_OK;
+  if (tiles >= (1ll << 31)) return fail(FSW_EINVAL, "too many tiles");
+  cudaError_t e;
+  if (cg == 2) {
+    const int pairs = (int)(tiles < d->max_pairs ? tiles : d->max_pairs);
+    e = launch_cg<MODE, 2>(p, 2 * pairs, dtype, acc16, st);
+  } else {
+    const int ctas = (int)(tiles < d->sm_count ? tiles : d->sm_count);
+    e = launch_cg<MODE, 1>(p, ctas, dtype, acc16, st);
+  }
+  if (e != cudaSuccess) return fail(FSW_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+  return FSW_OK;
+}
+
+// ------------------------------------------------ gate-gradient elementwise --
+// du = dout * silu(g); dg = (dout * u) * silu'(g).  g is upcast to fp32 for the
+// sigmoid; silu, silu' and every product are rounded to the 16-bit type, as in
+// the reference kernel.
+template <typename T>
+__device__ __forceinline__ void gate_grad_one(float dout, float g, float u, float& dg, float& du) {
+  const float sg = sigmoid_f32(g);
+  const float silu = round16<T>(g * sg);
+  const float dsilu = round16<T>(sg + g * sg * (1.0f - sg));
+  du = round16<T>(dout * silu);
+  dg = round16<T>(round16<T>(dout * u) * dsilu);
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) {
+  return __half2float(v);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) gate_grad_kernel(const T* __restrict__ dout,
+                                                       const T* __restrict__ g,
+                                                       const T* __restrict__ u, T* __restrict__ dg,
+                                                       T* __restrict__ du, int64_t numel) {
+  const int64_t nvec = numel >> 3;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    const uint4 vd = __ldg(reinterpret_cast<const uint4*>(dout) + v);
+    const uint4 vg = __ldg(reinterpret_cast<const uint4*>(g) + v);
+    const uint4 vu = __ldg(reinterpret_cast<const uint4*>(u) + v);
+    const T* pd = reinterpret_cast<const T*>(&vd);
+    const T* pg = reinterpret_cast<const T*>(&vg);
+    const T* pu = reinterpret_cast<const T*>(&vu);
+    uint4 odg, odu;
+    uint32_t* wdg = reinterpret_cast<uint32_t*>(&odg);
+    uint32_t* wdu = reinterpret_cast<uint32_t*>(&odu);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float dg0, du0, dg1, du1;
+      gate_grad_one<T>(to_f32(pd[2 * e]), to_f32(pg[2 * e]), to_f32(pu[2 * e]), dg0, du0);
+      gate_grad_one<T>(to_f32(pd[2 * e + 1]), to_f32(pg[2 * e + 1]), to_f32(pu[2 * e + 1]), dg1,
+                       du1);
+      wdg[e] = pack2<T>(dg0, dg1);
+      wdu[e] = pack2<T>(du0, du1);
+    }
+    reinterpret_cast<uint4*>(dg)[v] = odg;
+    reinterpret_cast<uint4*>(du)[v] = odu;
+  }
+  // tail of fewer than 8 elements
+  if (blockIdx.x == 0 && threadIdx.x < (numel & 7)) {
+    const int64_t i = (nvec << 3) + threadIdx.x;
+    float dgv, duv;
+    gate_grad_one<T>(to_f32(dout[i]), to_f32(g[i]), to_f32(u[i]), dgv, duv);
+    const uint32_t a = pack2<T>(dgv, 0.f), b = pack2<T>(duv, 0.f);
+    reinterpret_cast<unsigned short*>(dg)[i] = static_cast<unsigned short>(a & 0xFFFFu);
+    reinterpret_cast<unsigned short*>(du)[i] = static_cast<unsigned short>(b & 0xFFFFu);
+  }
+}
+
+}  // namespace fsw
+
+using namespace fsw;
+
+// ===================================================================== C ABI ==
+extern "C" {
+
+const char* fsw_last_error(void) { return t_err; }
+
+int fsw_query_device(int device, int* sm_count, int* cc_major, int* cc_minor,
+                     int64_t* smem_optin_bytes) {
+  int n = 0, maj = 0, min = 0, smem = 0;
+  FSW_CUDA(cudaDeviceGetAttribute(&maj, cudaDevAttrComputeCapabilityMajor, device));
+  FSW_CUDA(cudaDeviceGetAttribute(&min, cudaDevAttrComputeCapabilityMinor, device));
+  FSW_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device));
+  FSW_CUDA(cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+  if (sm_count) *sm_count = n;
+  if (cc_major) *cc_major = maj;
+  if (cc_minor) *cc_minor = min;
+  if (smem_optin_bytes) *smem_optin_bytes = smem;
+  if (maj != 10)
+    return fail(FSW_EDEVICE,
+                "device %d is compute capability %d.%d; this library runs on 10.x (B200) only",
+                device, maj, min);
+  return FSW_OK;
+}
+
+int64_t fsw_status(void) {
+  DeviceInfo* d = nullptr;
+  int rc = ensure_device(&d);
+  if (rc != FSW_OK) return rc;
+  FSW_CUDA(cudaDeviceSynchronize());
+  uint32_t v = 0, zero = 0;
+  FSW_CUDA(cudaMemcpy(&v, d->status, sizeof(v), cudaMemcpyDeviceToHost));
+  if (v != 0) {
+    FSW_CUDA(cudaMemcpy(d->status, &zero, sizeof(zero), cudaMemcpyHostToDevice));
+    fail(FSW_ETIMEOUT, "a kernel gave up on a bounded wait: code %u in CTA %u", v & 0xFFu, v >> 8);
+  }
+  return (int64_t)v;
+}
+
+int fsw_set_option(const char* name, int64_t value) {
+  if (name == nullptr) return fail(FSW_EINVAL, "option name is NULL");
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!strcmp(name, "cta_group")) {
+    if (value != 1 && value != 2) return fail(FSW_EINVAL, "cta_group must be 1 or 2");
+    g_opt.cta_group = value;
+  } else if (!strcmp(name, "group_m")) {
+    if (value < 1 || value > (1 << 20)) return fail(FSW_EINVAL, "group_m must be >= 1");
+    g_opt.group_m = value;
+  } else if (!strcmp(name, "k_lbo")) {
+    g_opt.k_lbo = value;
+  } else if (!strcmp(name, "k_sbo")) {
+    g_opt.k_sbo = value;
+  } else if (!strcmp(name, "k_kadv")) {
+    g_opt.k_kadv = value;
+  } else if (!strcmp(name, "mn_lbo")) {
+    g_opt.mn_lbo = value;
+  } else if (!strcmp(name, "mn_sbo")) {
+    g_opt.mn_sbo = value;
+  } else if (!strcmp(name, "mn_kadv")) {
+    g_opt.mn_kadv = value;
+  } else {
+    return fail(FSW_EINVAL, "unknown option '%s'", name);
+  }
+  return FSW_OK;
+}
+
+int64_t fsw_get_option(const char* name) {
+  if (name == nullptr) return -1;
+  if (!strcmp(name, "cta_group")) return g_opt.cta_group;
+  if (!strcmp(name, "group_m")) return g_opt.group_m;
+  if (!strcmp(name, "k_lbo")) return g_opt.k_lbo;
+  if (!strcmp(name, "k_sbo")) return g_opt.k_sbo;
+  if (!strcmp(name, "k_kadv")) return g_opt.k_kadv;
+  if (!strcmp(name, "mn_lbo")) return g_opt.mn_lbo;
+  if (!strcmp(name, "mn_sbo")) return g_opt.mn_sbo;
+  if (!strcmp(name, "mn_kadv")) return g_opt.mn_kadv;
+  return -1;
+}
+
+int fsw_forward(const void* x, const void* w_gate, const void* w_up, void* out, void* g, void* u,
+                int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream) {
+  int rc = check_common(T, dm, di, dtype, accum);
+  if (rc != FSW_OK) return rc;
+  if (!x || !w_gate || !w_up || !out) return fail(FSW_EINVAL, "x, w_gate, w_up and out are required");
+  if ((g == nullptr) != (u == nullptr))
+    return fail(FSW_EINVAL, "g and u must both be given or both be NULL");
+  if (!aligned16(x) || !aligned16(w_gate) || !aligned16(w_up) || !aligned16(out) || !aligned16(g) ||
+      !aligned16(u))
+    return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
+  DeviceInfo* d = nullptr;
+  if ((rc = ensure_device(&d)) != FSW_OK) return rc;
+  if (T == 0) return FSW_OK;
+  const int cg = (int)g_opt.cta_group;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  if ((rc = make_map(&p.a0, x, dtype, dm, T, 128, "x")) != FSW_OK) return rc;
+  p.a1 = p.a0;
+  if ((rc = make_map(&p.b0, w_gate, dtype, di, dm, 64, "w_gate")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.b1, w_up, dtype, di, dm, 64, "w_up")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.c0, g ? g : out, dtype, di, T, 32, "g")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.c1, u ? u : out, dtype, di, T, 32, "u")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.c2, out, dtype, di, T, 32, "out")) != FSW_OK) return rc;
+  (void)cg;
+  p.M = (int)T;
+  p.N = (int)di;
+  p.num_k_blocks = (int)((dm + 63) / 64);
+  p.store_gu = g != nullptr;
+  return run_gemm<MODE_FWD>(p, (int)T, dtype, accum == FSW_ACC_F16,
+                            static_cast<cudaStream_t>(stream), d);
+}
+
+int fsw_backward_elementwise(const void* dout, const void* g, const void* u, void* dg, void* du,
+                             int64_t numel, int dtype, void* stream) {
+  if (dtype != FSW_BF16 && dtype != FSW_FP16) return fail(FSW_EINVAL, "unknown dtype %d", dtype);
+  if (numel < 0) return fail(FSW_EINVAL, "numel < 0");
+  if (numel == 0) return FSW_OK;
+  if (!dout || !g || !u || !dg || !du) return fail(FSW_EINVAL, "NULL pointer");
+  if (!aligned16(dout) || !aligned16(g) || !aligned16(u) || !aligned16(dg) || !aligned16(du))
+    return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
+  DeviceInfo* d = nullptr;
+  int rc = ensure_device(&d);
+  if (rc != FSW_OK) return rc;
+  const int64_t nvec = numel >> 3;
+  int64_t blocks = (nvec + 255) / 256;
+  const int64_t cap = (int64_t)d->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FSW_BF16)
+    gate_grad_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(g),
+        static_cast<const __nv_bfloat16*>(u), static_cast<__nv_bfloat16*>(dg),
+        static_cast<__nv_bfloat16*>(du), numel);
+  else
+    gate_grad_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const __half*>(dout), static_cast<const __half*>(g),
+        static_cast<const __half*>(u), static_cast<__half*>(dg), static_cast<__half*>(du), numel);
+  FSW_CUDA(cudaGetLastError());
+  return FSW_OK;
+}
+
+int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const void* w_up, void* dx,
+                    int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream) {
+  int rc = check_common(T, dm, di, dtype, accum);
+  if (rc != FSW_OK) return rc;
+  if (!dg || !du || !w_gate || !w_up || !dx) return fail(FSW_EINVAL, "NULL pointer");
+  if (!aligned16(dg) || !aligned16(du) || !aligned16(w_gate) || !aligned16(w_up) || !aligned16(dx))
+    return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
+  DeviceInfo* d = nullptr;
+  if ((rc = ensure_device(&d)) != FSW_OK) return rc;
+  if (T == 0) return FSW_OK;
+  const int cg = (int)g_opt.cta_group;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  if ((rc = make_map(&p.a0, dg, dtype, di, T, 128, "dg")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.a1, du, dtype, di, T, 128, "du")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.b0, w_gate, dtype, di, dm, 256 / cg, "w_gate")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.b1, w_up, dtype, di, dm, 256 / cg, "w_up")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.c0, dx, dtype, dm, T, 32, "dx")) != FSW_OK) return rc;
+  p.c1 = p.c0;
+  p.c2 = p.c0;
+  p.M = (int)T;
+  p.N = (int)dm;
+  p.num_k_blocks = (int)((di + 63) / 64);
+  return run_gemm<MODE_DX>(p, (int)T, dtype, accum == FSW_ACC_F16,
+                           static_cast<cudaStream_t>(stream), d);
+}
+
+int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate, void* dw_up,
+                    int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream) {
+  int rc = check_common(T, dm, di, dtype, accum);
+  if (rc != FSW_OK) return rc;
+  if (!dw_gate || !dw_up) return fail(FSW_EINVAL, "NULL pointer");
+  if (!aligned16(x) || !aligned16(dg) || !aligned16(du) || !aligned16(dw_gate) || !aligned16(dw_up))
+    return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
+  DeviceInfo* d = nullptr;
+  if ((rc = ensure_device(&d)) != FSW_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (T == 0) {
+    // An empty reduction: the gradients are exactly zero.
+    FSW_CUDA(cudaMemsetAsync(dw_gate, 0, (size_t)dm * di * 2, st));
+    FSW_CUDA(cudaMemsetAsync(dw_up, 0, (size_t)dm * di * 2, st));
+    return FSW_OK;
+  }
+  if (!x || !dg || !du) return fail(FSW_EINVAL, "NULL pointer");
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  if ((rc = make_map(&p.a0, x, dtype, dm, T, 64, "x^T")) != FSW_OK) return rc;
+  p.a1 = p.a0;
+  if ((rc = make_map(&p.b0, dg, dtype, di, T, 64, "dg")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.b1, du, dtype, di, T, 64, "du")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.c0, dw_gate, dtype, di, dm, 32, "dw_gate")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.c1, dw_up, dtype, di, dm, 32, "dw_up")) != FSW_OK) return rc;
+  p.c2 = p.c0;
+  p.M = (int)dm;
+  p.N = (int)di;
+  p.num_k_blocks = (int)((T + 63) / 64);
+  return run_gemm<MODE_DW>(p, (int)dm, dtype, accum == FSW_ACC_F16, st, d);
+}
+
+int fsw_backward(const void* dout, const void* x, const void* w_gate, const void* w_up,
+                 const void* g, const void* u, void* dg_scratch, void* du_scratch, void* dx,
+                 void* dw_gate, void* dw_up, int64_t T, int64_t dm, int64_t di, int dtype,
+                 int accum, void* stream) {
+  int rc = check_common(T, dm, di, dtype, accum);
+  if (rc != FSW_OK) return rc;
+  if ((rc = fsw_backward_elementwise(dout, g, u, dg_scratch, du_scratch, T * di, dtype, stream)) !=
+      FSW_OK)
+    return rc;
+  if ((rc = fsw_backward_dx(dg_scratch, du_scratch, w_gate, w_up, dx, T, dm, di, dtype,
+                            FSW_ACC_F32, stream)) != FSW_OK)
+    return rc;
+  return fsw_backward_dw(x, dg_scratch, du_scratch, dw_gate, dw_up, T, dm, di, dtype, accum,
+                         stream);
+}
+
+}  // extern "C"

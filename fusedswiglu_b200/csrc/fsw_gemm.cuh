@@ -1,0 +1,482 @@
+// Persistent, warp-specialised tcgen05 GEMM used by all three tensor-core
+// phases of fused SwiGLU on sm_100a.
+//
+//   MODE_FWD : [g | u] = x @ [W_gate | W_up]         (A K-major, B MN-major)
+//              epilogue writes g, u and out = silu(g) * u
+//   MODE_DX  : dX = dg @ W_gate^T + du @ W_up^T      (A K-major, B K-major)
+//              one accumulator, the K loop runs over both products
+//   MODE_DW  : [dW_gate | dW_up] = x^T @ [dg | du]   (A MN-major, B MN-major)
+//
+// One CTA owns 128 accumulator rows x 256 fp32 columns of tensor memory, twice
+// (two accumulator stages), so the epilogue of tile i overlaps the MMAs of tile
+// i+1.  With CG == 2 two CTAs of a cluster form a pair: each stages its own 128
+// rows of A and half (128) of the 256 B columns, the pair leader issues
+// M=256 x N=256 MMAs that read both CTAs' shared memory and write both CTAs'
+// tensor memory.  No TMA multicast is used anywhere.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner and MMA
+// issuer, warps 2..5 = epilogue (TMEM -> registers -> swizzled smem -> TMA store).
+//
+// Every mbarrier wait is bounded: after kWaitLimitNs the waiting warp records a
+// code in `status`, raises the CTA's abort flag and every role leaves its loop;
+// the CTA then lets in-flight copies drain, frees its tensor memory and returns.
+#pragma once
+
+#include "fsw_ptx.cuh"
+
+namespace fsw {
+
+enum : int { MODE_FWD = 0, MODE_DX = 1, MODE_DW = 2 };
+enum : int { MAJOR_K = 0, MAJOR_MN = 1 };
+
+// Codes written to the status word when a bounded wait gives up.
+enum : uint32_t {
+  WAIT_OK = 0,
+  WAIT_PRODUCER_EMPTY = 1,
+  WAIT_MMA_FULL = 2,
+  WAIT_MMA_TMEM_EMPTY = 3,
+  WAIT_EPI_TMEM_FULL = 4,
+};
+
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait
+constexpr uint64_t kDrainNs = 20000000ull;        // 20 ms drain on the abort path
+
+struct GemmParams {
+  CUtensorMap a0, a1;      // A operand(s); a1 only in MODE_DX (second product)
+  CUtensorMap b0, b1;      // B operands (gate, up)
+  CUtensorMap c0, c1, c2;  // outputs (see the mode table above)
+  uint64_t a_desc, b_desc; // UMMA shared-memory descriptors with a zero start address
+  uint32_t a_kadv, b_kadv; // bytes to advance the start address per K=16 step
+  uint32_t idesc;          // UMMA instruction descriptor
+  int M, N;                // output extents: rows, columns (per output tensor)
+  int num_m_tiles, num_n_tiles, group_m;
+  int num_k_blocks;        // 64-wide K blocks per product
+  int store_gu;            // MODE_FWD: also write g and u
+  uint32_t* status;        // device status word (0 = ok)
+};
+
+template <int MODE, int CG>
+struct TileCfg {
+  static constexpr int A_MAJOR = (MODE == MODE_DW) ? MAJOR_MN : MAJOR_K;
+  static constexpr int B_MAJOR = (MODE == MODE_DX) ? MAJOR_K : MAJOR_MN;
+  static constexpr int BM = 128;          // accumulator rows per CTA
+  static constexpr int BN = 256;          // accumulator columns per CTA (MMA N)
+  static constexpr int BK = 64;           // one 128-byte swizzle row of 16-bit elements
+  static constexpr int B_ROWS = BN / CG;  // B n-extent staged by each CTA
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = B_ROWS * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (CG == 1) ? 3 : 5;
+  static constexpr int CHUNK_BYTES = 64 * BK * 2;  // one MN-major 64x64 box
+  static constexpr int EPI_WARPS = 4;
+  static constexpr int EPI_NBUF = 3;
+  static constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows x 64 16-bit columns
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_NBUF * EPI_BUF_BYTES;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;
+  static constexpr int THREADS = 192;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int NSEG = (MODE == MODE_DX) ? 2 : 1;
+  // Output columns covered by one tile, per output tensor.
+  static constexpr int TILE_N = (MODE == MODE_DX) ? 256 : 128;
+  static constexpr int TILE_M = BM * CG;
+};
+
+// ------------------------------------------------------------- conversions --
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <typename T>
+__device__ __forceinline__ float round16(float v);
+template <>
+__device__ __forceinline__ float round16<__nv_bfloat16>(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+template <>
+__device__ __forceinline__ float round16<__half>(float v) {
+  return __half2float(__float2half_rn(v));
+}
+
+__device__ __forceinline__ float sigmoid_f32(float x) { return __frcp_rn(1.0f + __expf(-x)); }
+
+// ------------------------------------------------------------ bounded wait --
+struct AbortCtl {
+  volatile uint32_t* flag;  // shared-memory abort flag of this CTA
+  uint32_t* status;         // global status word
+};
+
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const AbortCtl& ctl,
+                                             uint32_t code) {
+  bool ok = ptx::mbar_try_wait(bar, parity);
+  if (!ok) {
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+      if (ptx::mbar_try_wait(bar, parity)) {
+        ok = true;
+        break;
+      }
+      if ((++spins & 255u) == 0u) {
+        if (*ctl.flag != 0u) break;
+        if (ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
+          *ctl.flag = code;
+          atomicCAS(ctl.status, 0u, code | (static_cast<uint32_t>(blockIdx.x) << 8));
+          break;
+        }
+      }
+    }
+  }
+  return __all_sync(0xffffffffu, ok);
+}
+
+// Linear tile index -> (m_tile, n_tile); m is grouped so that concurrently
+// running tiles share A row panels and B column panels in L2.
+__device__ __forceinline__ void decode_tile(int t, const GemmParams& p, int& m_tile, int& n_tile) {
+  const int per_group = p.group_m * p.num_n_tiles;
+  const int g = t / per_group;
+  const int first_m = g * p.group_m;
+  const int gsz = min(p.num_m_tiles - first_m, p.group_m);
+  const int r = t - g * per_group;
+  m_tile = first_m + r % gsz;
+  n_tile = r / gsz;
+}
+
+// ------------------------------------------------------------------ kernel --
+template <int MODE, int CG, typename T, bool ACC16>
+__global__ void __launch_bounds__(192, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
+  using C = TileCfg<MODE, CG>;
+  constexpr int STAGES = C::STAGES;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
+  const uint32_t smem_base = (raw_u32 + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - raw_u32);
+
+  const uint32_t epi_base = smem_base + STAGES * C::STAGE_BYTES;
+  const uint32_t bar_base = epi_base + C::EPI_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t misc_off = (bar_base - smem_base) + 8u * (2 * STAGES + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + misc_off);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + misc_off + 4);
+  const AbortCtl ctl{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (CG == 2) ? ptx::cluster_ctarank() : 0u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), C::EPI_WARPS * CG);
+    }
+    *abort_flag = 0u;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tensormap(&p.a0);
+    ptx::prefetch_tensormap(&p.b0);
+    ptx::prefetch_tensormap(&p.b1);
+    ptx::prefetch_tensormap(&p.c0);
+    if (MODE == MODE_DX) ptx::prefetch_tensormap(&p.a1);
+    if (MODE != MODE_DX) ptx::prefetch_tensormap(&p.c1);
+    if (MODE == MODE_FWD) ptx::prefetch_tensormap(&p.c2);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<CG>(bar_base + 8u * (2 * STAGES + 4), C::TMEM_COLS);
+    ptx::tmem_relinquish<CG>();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (CG == 2) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_clusters = gridDim.x / CG;
+  const int cluster_id = blockIdx.x / CG;
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int num_kb = p.num_k_blocks;
+
+  if (warp == 0) {
+    // ======================= TMA producer =======================
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    const uint32_t rank_off = cta_rank * C::B_ROWS;
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+      int m_tile, n_tile;
+      decode_tile(t, p, m_tile, n_tile);
+      const int m0 = m_tile * C::TILE_M + cta_rank * C::BM;
+      const int n0 = n_tile * C::TILE_N;
+      for (int seg = 0; seg < C::NSEG && ok; ++seg) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = bounded_wait(empty_bar(s), ph ^ 1u, ctl, WAIT_PRODUCER_EMPTY);
+          if (!ok) break;
+          if (lane == 0) {
+            const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
+            const uint32_t b_dst = a_dst + C::A_BYTES;
+            const int k0 = kb * C::BK;
+            uint32_t fb = full_bar(s);
+            if (CG == 2) fb = ptx::mapa(fb, 0);
+            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), CG * C::STAGE_BYTES);
+            auto load = [&](uint32_t dst, const CUtensorMap* tm, int x, int y) {
+              if (CG == 2)
+                ptx::tma_load_2d_pair(dst, tm, fb, x, y);
+              else
+                ptx::tma_load_2d(dst, tm, fb, x, y);
+            };
+            // ---- A tile: 128 rows x 64 k
+            if (C::A_MAJOR == MAJOR_K) {
+              load(a_dst, (MODE == MODE_DX && seg == 1) ? &p.a1 : &p.a0, k0, m0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < C::BM / 64; ++c)
+                load(a_dst + c * C::CHUNK_BYTES, &p.a0, m0 + c * 64, k0);
+            }
+            // ---- B tile: B_ROWS n x 64 k
+            if (C::B_MAJOR == MAJOR_K) {
+              load(b_dst, seg == 1 ? &p.b1 : &p.b0, k0, n0 + rank_off);
+            } else if (CG == 1) {
+#pragma unroll
+              for (int c = 0; c < 4; ++c)
+                load(b_dst + c * C::CHUNK_BYTES, c < 2 ? &p.b0 : &p.b1, n0 + (c & 1) * 64, k0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < 2; ++c)
+                load(b_dst + c * C::CHUNK_BYTES, cta_rank ? &p.b1 : &p.b0, n0 + c * 64, k0);
+            }
+          }
+          __syncwarp();
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ======================= MMA issuer (pair leader only) =======================
+    if (cta_rank == 0) {
+      int s = 0, a = 0;
+      uint32_t ph = 0, aph = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        ok = bounded_wait(tempty_bar(a), aph ^ 1u, ctl, WAIT_MMA_TMEM_EMPTY);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + a * C::BN;
+        uint32_t accumulate = 0;
+        for (int it = 0; it < C::NSEG * num_kb; ++it) {
+          ok = bounded_wait(full_bar(s), ph, ctl, WAIT_MMA_FULL);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          if (lane == 0) {
+            const uint32_t a_addr = smem_base + s * C::STAGE_BYTES;
+            const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+            for (int k = 0; k < C::BK / 16; ++k) {
+              const uint64_t ad = p.a_desc | (((a_addr + k * p.a_kadv) & 0x3FFFFu) >> 4);
+              const uint64_t bd = p.b_desc | (((b_addr + k * p.b_kadv) & 0x3FFFFu) >> 4);
+              ptx::mma_f16_ss<CG>(d_tmem, ad, bd, p.idesc, accumulate);
+              accumulate = 1;
+            }
+            if (CG == 2)
+              ptx::mma_commit_pair(empty_bar(s), 3);
+            else
+              ptx::mma_commit(empty_bar(s));
+          }
+          __syncwarp();
+          accumulate = 1;
+          if (++s == STAGES) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (!ok) break;
+        if (lane == 0) {
+          if (CG == 2)
+            ptx::mma_commit_pair(tfull_bar(a), 3);
+          else
+            ptx::mma_commit(tfull_bar(a));
+        }
+        __syncwarp();
+        a ^= 1;
+        if (a == 0) aph ^= 1u;
+      }
+    }
+  } else {
+    // ======================= epilogue =======================
+    const int q = warp & 3;     // TMEM lane quadrant this warp may read
+    const int ew = warp - 2;    // staging-buffer owner index
+    const uint32_t my_epi = epi_base + ew * C::EPI_NBUF * C::EPI_BUF_BYTES;
+    const uint32_t row_off = lane * 128u;
+    const uint32_t sw = lane & 7u;
+    int a = 0, rb = 0;
+    uint32_t aph = 0;
+    bool ok = true;
+    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+      int m_tile, n_tile;
+      decode_tile(t, p, m_tile, n_tile);
+      const int row0 = m_tile * C::TILE_M + cta_rank * C::BM + q * 32;
+      const int n0 = n_tile * C::TILE_N;
+      ok = bounded_wait(tfull_bar(a), aph, ctl, WAIT_EPI_TMEM_FULL);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * C::BN;
+
+      auto release_tmem = [&]() {
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if (CG == 2)
+            ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(a), 0));
+          else
+            ptx::mbar_arrive(tempty_bar(a));
+        }
+      };
+
+      if (MODE == MODE_FWD) {
+        const uint32_t buf_g = my_epi, buf_u = my_epi + C::EPI_BUF_BYTES,
+                       buf_o = my_epi + 2 * C::EPI_BUF_BYTES;
+#pragma unroll 1
+        for (int jb = 0; jb < 2; ++jb) {
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            uint32_t rg[32], ru[32];
+            ptx::tmem_ld_32x32(taddr + jb * 64 + h * 32, rg);
+            ptx::tmem_ld_32x32(taddr + 128 + jb * 64 + h * 32, ru);
+            ptx::tmem_ld_wait();
+            if (jb == 1 && h == 1) release_tmem();
+            if (h == 0) {
+              if (lane == 0) ptx::tma_store_wait_read<0>();
+              __syncwarp();
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t pg[4], pu[4], po[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int c0 = i * 8 + e * 2;
+                if (ACC16) {
+                  // fp16 accumulators sit in the low half of each 32-bit column.
+                  const __half g0 = __ushort_as_half(static_cast<unsigned short>(rg[c0]));
+                  const __half g1 = __ushort_as_half(static_cast<unsigned short>(rg[c0 + 1]));
+                  const __half u0 = __ushort_as_half(static_cast<unsigned short>(ru[c0]));
+                  const __half u1 = __ushort_as_half(static_cast<unsigned short>(ru[c0 + 1]));
+                  const float gf0 = __half2float(g0), gf1 = __half2float(g1);
+                  const __half s0 = __float2half_rn(gf0 * sigmoid_f32(gf0));
+                  const __half s1 = __float2half_rn(gf1 * sigmoid_f32(gf1));
+                  const __half2 o = __hmul2(__halves2half2(u0, u1), __halves2half2(s0, s1));
+                  pg[e] = (rg[c0] & 0xFFFFu) | (rg[c0 + 1] << 16);
+                  pu[e] = (ru[c0] & 0xFFFFu) | (ru[c0 + 1] << 16);
+                  po[e] = *reinterpret_cast<const uint32_t*>(&o);
+                } else {
+                  const float g0 = __uint_as_float(rg[c0]), g1 = __uint_as_float(rg[c0 + 1]);
+                  const float u0 = __uint_as_float(ru[c0]), u1 = __uint_as_float(ru[c0 + 1]);
+                  const float s0 = round16<T>(g0 * sigmoid_f32(g0));
+                  const float s1 = round16<T>(g1 * sigmoid_f32(g1));
+                  pg[e] = pack2<T>(g0, g1);
+                  pu[e] = pack2<T>(u0, u1);
+                  po[e] = pack2<T>(u0 * s0, u1 * s1);
+                }
+              }
+              const uint32_t off = row_off + (((h * 4 + i) ^ sw) << 4);
+              ptx::st_shared_v4(buf_g + off, pg[0], pg[1], pg[2], pg[3]);
+              ptx::st_shared_v4(buf_u + off, pu[0], pu[1], pu[2], pu[3]);
+              ptx::st_shared_v4(buf_o + off, po[0], po[1], po[2], po[3]);
+            }
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          const int col = n0 + jb * 64;
+          if (lane == 0 && row0 < p.M && col < p.N) {
+            if (p.store_gu) {
+              ptx::tma_store_2d(&p.c0, buf_g, col, row0);
+              ptx::tma_store_2d(&p.c1, buf_u, col, row0);
+            }
+            ptx::tma_store_2d(&p.c2, buf_o, col, row0);
+            ptx::tma_store_commit();
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int jb = 0; jb < 4; ++jb) {
+          uint32_t r0[32], r1[32];
+          ptx::tmem_ld_32x32(taddr + jb * 64, r0);
+          ptx::tmem_ld_32x32(taddr + jb * 64 + 32, r1);
+          ptx::tmem_ld_wait();
+          if (jb == 3) release_tmem();
+          if (lane == 0) ptx::tma_store_wait_read<C::EPI_NBUF - 1>();
+          __syncwarp();
+          const uint32_t buf = my_epi + rb * C::EPI_BUF_BYTES;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int c0 = (i & 3) * 8 + e * 2;
+              const uint32_t v0 = (i < 4) ? r0[c0] : r1[c0];
+              const uint32_t v1 = (i < 4) ? r0[c0 + 1] : r1[c0 + 1];
+              if (ACC16)
+                pk[e] = (v0 & 0xFFFFu) | (v1 << 16);
+              else
+                pk[e] = pack2<T>(__uint_as_float(v0), __uint_as_float(v1));
+            }
+            ptx::st_shared_v4(buf + row_off + ((i ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          const int col = (MODE == MODE_DX) ? (n0 + jb * 64) : (n0 + (jb & 1) * 64);
+          if (lane == 0) {
+            if (row0 < p.M && col < p.N)
+              ptx::tma_store_2d((MODE == MODE_DW && jb >= 2) ? &p.c1 : &p.c0, buf, col, row0);
+            ptx::tma_store_commit();
+          }
+          rb = (rb + 1 == C::EPI_NBUF) ? 0 : rb + 1;
+        }
+      }
+      a ^= 1;
+      if (a == 0) aph ^= 1u;
+    }
+    if (lane == 0) ptx::tma_store_wait_all<0>();
+    __syncwarp();
+  }
+
+  // ======================= teardown =======================
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0u) {
+    // A wait gave up: give copies and MMAs still in flight time to land before
+    // shared and tensor memory are handed back.
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < kDrainNs) __nanosleep(1000);
+  }
+  if (CG == 2) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc<CG>(tmem_base, C::TMEM_COLS);
+  }
+}
+
+}  // namespace fsw

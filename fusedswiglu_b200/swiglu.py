@@ -1,0 +1,24 @@
+"""``FusedSwiGLU``: bf16 SwiGLU with fp32 accumulation on B200 tensor cores.
+
+Drop-in for the reference's ``fused_swiglu.swiglu.FusedSwiGLU``
+(fused_swiglu/swiglu.py:16-58): ``FusedSwiGLU.apply(x, w_gate, w_up)`` with
+x (bs, sq, d_model) and weights (d_model, d_intermediate)."""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+
+from . import _autograd
+
+
+class FusedSwiGLU(Function):
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
+    def forward(ctx, input: torch.Tensor, weight_gate: torch.Tensor, weight_up: torch.Tensor) -> torch.Tensor:
+        assert input.dtype == torch.bfloat16, "Expected torch.bfloat16 inputs and weights."
+        return _autograd.swiglu_forward(ctx, input, weight_gate, weight_up, fast_accum=False)
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, grad_output):
+        return _autograd.swiglu_backward(ctx, grad_output, fast_accum=False)

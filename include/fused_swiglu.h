@@ -1,0 +1,119 @@
+/*
+ * C ABI of libfused_swiglu_sm100.so: fused SwiGLU forward and backward for
+ * NVIDIA B200 (sm_100a), hand-written TMA + tcgen05 kernels.
+ *
+ * This header is the drop-in boundary for the GPU work that the Python package
+ * `fused_swiglu` (fattorib/fusedswiglu) performs through Triton and cuBLAS.  Each
+ * entry point names the reference interface it replaces, by file:line within
+ * that project.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer on the current CUDA device, 16-byte
+ *     aligned, to a dense row-major array; the library allocates nothing;
+ *   - T = batch * sequence tokens, dm = d_model, di = d_intermediate;
+ *     x is (T, dm); w_gate and w_up are (dm, di); g, u, out, dout are (T, di);
+ *     dm and di must be multiples of 8 (16-byte rows); T may be any value >= 0;
+ *   - dtype: FSW_BF16 or FSW_FP16 is the storage type of every tensor;
+ *     accum: FSW_ACC_F32, or FSW_ACC_F16 (fp16 tensors only) for an fp16
+ *     tensor-memory accumulator;
+ *   - `stream` is a cudaStream_t passed as void*; all work is asynchronous on it;
+ *   - return value: FSW_OK or a negative FSW_E* code; fsw_last_error() gives the
+ *     message for the calling thread.  Nothing aborts or throws.
+ */
+#ifndef FUSED_SWIGLU_H_
+#define FUSED_SWIGLU_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { FSW_BF16 = 0, FSW_FP16 = 1 };
+enum { FSW_ACC_F32 = 0, FSW_ACC_F16 = 1 };
+enum {
+  FSW_OK = 0,
+  FSW_EINVAL = -1,      /* bad pointer, shape, dtype or accumulate mode          */
+  FSW_EDEVICE = -2,     /* current device is not compute capability 10.x         */
+  FSW_ECUDA = -3,       /* a CUDA runtime or driver call failed                  */
+  FSW_ETIMEOUT = -4,    /* a kernel gave up on a bounded wait (see fsw_status)   */
+  FSW_EUNAVAILABLE = -5 /* the driver lacks cuTensorMapEncodeTiled               */
+};
+
+/*
+ * Forward:  g = x @ w_gate, u = x @ w_up, out = silu(g) * u, one dual GEMM.
+ * Replaces fused_swiglu_fwd + swiglu_kernel (fused_swiglu/kernels/kernels_bf16.py:41-206,
+ * fused_swiglu/kernels/kernels_fp16.py:41-216).  `g` and `u` may both be NULL to
+ * skip saving the activations (inference); `out` is required.
+ * accum = FSW_ACC_F16 corresponds to fast_accum=True (kernels_fp16.py:69-75).
+ */
+int fsw_forward(const void* x, const void* w_gate, const void* w_up, void* out, void* g, void* u,
+                int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream);
+
+/*
+ * Gate-gradient elementwise step: du = dout * silu(g), dg = dout * u * silu'(g),
+ * with the reference's rounding points.  Replaces elementwise_backward +
+ * elementwise_backward_kernel (kernels_bf16.py:210-255, kernels_fp16.py:220-265).
+ * Unlike the reference launcher it also processes a tail of numel % 128 elements.
+ */
+int fsw_backward_elementwise(const void* dout, const void* g, const void* u, void* dg, void* du,
+                             int64_t numel, int dtype, void* stream);
+
+/*
+ * Input gradient: dx = dg @ w_gate^T + du @ w_up^T as ONE accumulated GEMM.
+ * Replaces the two cuBLAS matmuls and the add at fused_swiglu/swiglu.py:45.
+ */
+int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const void* w_up, void* dx,
+                    int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream);
+
+/*
+ * Weight gradients: dw_gate = x^T @ dg, dw_up = x^T @ du, reduced over all T
+ * tokens in one dual GEMM.  Replaces fused_bmm + bmm_kernel
+ * (kernels_bf16.py:280-412, kernels_fp16.py:290-422) and the batch sum
+ * `unbroadcast` (fused_swiglu/swiglu.py:11-13,56-57).
+ */
+int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate, void* dw_up,
+                    int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream);
+
+/*
+ * Whole backward on one stream: elementwise step into the caller's scratch
+ * (`dg_scratch`, `du_scratch`, each T*di elements), then dx, then dw.
+ * Replaces FusedSwiGLU.backward (fused_swiglu/swiglu.py:34-58).
+ * accum applies to the dw GEMM; dx always accumulates in fp32, as cuBLAS does on
+ * the reference path.
+ */
+int fsw_backward(const void* dout, const void* x, const void* w_gate, const void* w_up,
+                 const void* g, const void* u, void* dg_scratch, void* du_scratch, void* dx,
+                 void* dw_gate, void* dw_up, int64_t T, int64_t dm, int64_t di, int dtype,
+                 int accum, void* stream);
+
+/* Message for the last non-zero return on the calling thread ("" if none). */
+const char* fsw_last_error(void);
+
+/*
+ * Device facts for `device`: SM count, compute capability, opt-in shared memory
+ * per block.  Any output pointer may be NULL.  Returns FSW_EDEVICE if the device
+ * is not compute capability 10.x (there is no fallback path).
+ */
+int fsw_query_device(int device, int* sm_count, int* cc_major, int* cc_minor,
+                     int64_t* smem_optin_bytes);
+
+/*
+ * Synchronises the current device and returns the kernels' status word, clearing
+ * it: 0 when every bounded wait completed, otherwise (cta << 8 | code) of the
+ * first wait that gave up.  Returns a negative FSW_E* code on CUDA failure.
+ */
+int64_t fsw_status(void);
+
+/*
+ * Tuning and debugging knobs, process-wide.  Known names: "cta_group" (1 or 2),
+ * "group_m" (tile-rasterisation group height, in tiles).  Returns FSW_EINVAL for
+ * an unknown name or value.  fsw_get_option returns the current value or -1.
+ */
+int fsw_set_option(const char* name, int64_t value);
+int64_t fsw_get_option(const char* name);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FUSED_SWIGLU_H_ */
