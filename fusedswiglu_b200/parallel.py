@@ -1,0 +1,107 @@
+"""Column-parallel SwiGLU across the GPUs of one node.
+
+``d_intermediate`` is split evenly over the ranks of a ``torch.distributed``
+process group (one process per GPU).  Rank r holds columns
+``[r*di/P, (r+1)*di/P)`` of W_gate and W_up and every rank holds the whole x, so
+
+  * forward is purely local: rank r produces its slice ``out[..., r*di/P:(r+1)*di/P]``;
+  * backward is local for dW_gate/dW_up (their column slices) and produces a
+    PARTIAL dX on every rank; the one collective on the path is the all-reduce
+    (sum) of dX.  It is started as soon as the dX GEMM has been queued and runs on
+    NCCL's stream while the dW GEMM - which does not depend on dX - computes; the
+    backward joins the two before it returns.
+
+The reference (fattorib/fusedswiglu) has no multi-GPU mode; this follows the
+standard tensor-parallel MLP split and keeps the single-GPU numerics per shard.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+from torch.autograd import Function
+
+from . import _launch
+
+
+def shard_bounds(d_intermediate: int, rank: int, world_size: int) -> Tuple[int, int]:
+    """Column range of `rank`; d_intermediate must split into equal 8-aligned parts."""
+    if world_size < 1 or not (0 <= rank < world_size):
+        raise ValueError(f"bad rank {rank} for world size {world_size}")
+    if d_intermediate % world_size != 0:
+        raise ValueError(f"d_intermediate={d_intermediate} is not divisible by world_size={world_size}")
+    per = d_intermediate // world_size
+    if per % 8 != 0:
+        raise ValueError(
+            f"shard width {per} (= {d_intermediate}/{world_size}) must be a multiple of 8 (16-byte rows)"
+        )
+    return rank * per, (rank + 1) * per
+
+
+def shard_columns(w: torch.Tensor, rank: int, world_size: int) -> torch.Tensor:
+    """Contiguous copy of this rank's column slice of a (d_model, d_intermediate) weight."""
+    lo, hi = shard_bounds(w.shape[1], rank, world_size)
+    return w[:, lo:hi].contiguous()
+
+
+def unshard_columns(shard: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather column slices (last dimension) back into the full tensor."""
+    world = dist.get_world_size(group)
+    parts = [torch.empty_like(shard) for _ in range(world)]
+    dist.all_gather(parts, shard.contiguous(), group=group)
+    return torch.cat(parts, dim=-1)
+
+
+class _CudaBackend:
+    """The product compute path: C-ABI launches on the current CUDA stream."""
+
+    forward = staticmethod(_launch.forward)
+    gate_grad = staticmethod(_launch.gate_grad)
+    grad_input = staticmethod(_launch.grad_input)
+    grad_weights = staticmethod(_launch.grad_weights)
+
+
+class ColumnParallelSwiGLU(Function):
+    """``ColumnParallelSwiGLU.apply(x, w_gate_shard, w_up_shard, group=None)``.
+
+    x: (bs, sq, d_model), identical on every rank.  Weight shards:
+    (d_model, d_intermediate / world_size).  Returns this rank's slice of out.
+    The gradient returned for x is the full, all-reduced dX."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate_shard, w_up_shard, group=None, fast_accum=False, backend=None):
+        backend = backend or _CudaBackend
+        assert x.ndim == 3 and w_gate_shard.ndim == 2, "Incorrect number of dimensions for LHS or RHS"
+        assert w_gate_shard.shape == w_up_shard.shape, "Expected both weight matrices to have same shape"
+        assert x.shape[2] == w_up_shard.shape[0], "Dimension mismatch between x and the weight shards"
+        bs, sq, dm = x.shape
+        x2d = x.contiguous().view(bs * sq, dm)
+        wg = w_gate_shard.contiguous()
+        wu = w_up_shard.contiguous()
+        out, g, u = backend.forward(x2d, wg, wu, fast_accum=fast_accum, save_activations=True)
+        ctx.save_for_backward(x2d, wg, wu, g, u)
+        ctx.meta = (bs, sq, dm, group, fast_accum, backend)
+        return out.view(bs, sq, wg.shape[1])
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x2d, wg, wu, g, u = ctx.saved_tensors
+        bs, sq, dm, group, fast_accum, backend = ctx.meta
+        dout = grad_output.contiguous().view(bs * sq, wg.shape[1])
+        dg, du = backend.gate_grad(dout, g, u)
+        dx = backend.grad_input(dg, du, wg, wu)
+        work = None
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            work = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group, async_op=True)
+        dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=fast_accum)
+        if work is not None:
+            work.wait()
+        return dx.view(bs, sq, dm), dwg, dwu, None, None, None
+
+
+def column_parallel_swiglu(
+    x: torch.Tensor, w_gate_shard: torch.Tensor, w_up_shard: torch.Tensor,
+    group: Optional[dist.ProcessGroup] = None, fast_accum: bool = False,
+) -> torch.Tensor:
+    return ColumnParallelSwiGLU.apply(x, w_gate_shard, w_up_shard, group, fast_accum, None)

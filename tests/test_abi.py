@@ -1,0 +1,72 @@
+"""The C-ABI shared library loads without a GPU and exports exactly what
+include/fused_swiglu.h declares; argument checking works before any CUDA call."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from fusedswiglu_b200 import _lib
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "fused_swiglu.h"
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(fsw_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_functions()
+    for required in ("fsw_forward", "fsw_backward_elementwise", "fsw_backward_dx", "fsw_backward_dw",
+                     "fsw_backward", "fsw_last_error", "fsw_query_device", "fsw_status"):
+        assert required in names
+
+
+def test_library_exports_every_declared_symbol(built_library):
+    lib = ctypes.CDLL(str(built_library))
+    for name in declared_functions():
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+
+
+def test_binding_table_covers_the_header():
+    assert sorted(_lib.SIGNATURES) == declared_functions()
+
+
+def test_header_has_no_torch_or_cxx_types():
+    text = HEADER.read_text()
+    assert "torch" not in text.lower() and "std::" not in text and "at::" not in text
+    assert 'extern "C"' in text
+
+
+def test_argument_errors_are_reported_not_raised_across_the_abi():
+    lib = _lib.load()
+    # dtype 7 does not exist
+    rc = lib.fsw_forward(None, None, None, None, None, None, 8, 64, 64, 7, 0, None)
+    assert rc == -1 and "dtype" in _lib.last_error()
+    # d_model not a multiple of 8
+    rc = lib.fsw_forward(None, None, None, None, None, None, 8, 60, 64, 0, 0, None)
+    assert rc == -1 and "multiples of 8" in _lib.last_error()
+    # fp16 accumulation with bf16 tensors
+    rc = lib.fsw_backward_dw(None, None, None, None, None, 8, 64, 64, 0, 1, None)
+    assert rc == -1 and "fp16" in _lib.last_error()
+    # NULL tensors
+    rc = lib.fsw_forward(None, None, None, None, None, None, 8, 64, 64, 0, 0, None)
+    assert rc == -1 and "required" in _lib.last_error()
+    # misaligned pointer
+    rc = lib.fsw_backward_elementwise(8, 16, 16, 16, 16, 64, 0, None)
+    assert rc == -1 and "aligned" in _lib.last_error()
+    with pytest.raises(_lib.FusedSwiGLUError):
+        _lib.check("fsw_forward", rc)
+
+
+def test_options_roundtrip():
+    old = _lib.get_option("group_m")
+    _lib.set_option("group_m", 4)
+    assert _lib.get_option("group_m") == 4
+    _lib.set_option("group_m", old)
+    with pytest.raises(_lib.FusedSwiGLUError):
+        _lib.set_option("cta_group", 3)
+    with pytest.raises(_lib.FusedSwiGLUError):
+        _lib.set_option("no_such_option", 1)
+    assert _lib.get_option("no_such_option") == -1

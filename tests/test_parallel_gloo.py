@@ -1,0 +1,164 @@
+"""Host logic of the column-parallel mode on CPU: two gloo ranks, with the GPU
+launches replaced by a CPU stand-in built from the oracle's torch formula.  The
+stand-in is test scaffolding; the product's backend is CUDA-only."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+REPO = Path(__file__).resolve().parent.parent
+
+
+class OracleBackend:
+    """CPU stand-in with the launchers' signatures, fp32 math on 16-bit tensors."""
+
+    @staticmethod
+    def forward(x2d, wg, wu, *, fast_accum=False, save_activations=True):
+        g = (x2d.float() @ wg.float()).to(x2d.dtype)
+        u = (x2d.float() @ wu.float()).to(x2d.dtype)
+        out = (torch.nn.functional.silu(g.float()) * u.float()).to(x2d.dtype)
+        return out, g, u
+
+    @staticmethod
+    def gate_grad(dout, g, u):
+        gf = g.float()
+        s = torch.sigmoid(gf)
+        du = (dout.float() * gf * s).to(dout.dtype)
+        dg = (dout.float() * u.float() * (s + gf * s * (1 - s))).to(dout.dtype)
+        return dg, du
+
+    @staticmethod
+    def grad_input(dg, du, wg, wu):
+        return (dg.float() @ wg.float().T + du.float() @ wu.float().T).to(dg.dtype)
+
+    @staticmethod
+    def grad_weights(x2d, dg, du, *, fast_accum=False):
+        return (x2d.float().T @ dg.float()).to(x2d.dtype), (x2d.float().T @ du.float()).to(x2d.dtype)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, str(REPO))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fusedswiglu_b200 import parallel
+        from oracle import swiglu_oracle as orc
+
+        torch.manual_seed(0)
+        bs, sq, dm, di = 2, 32, 64, 128
+        x = torch.randn(bs, sq, dm).bfloat16().requires_grad_(True)
+        wg = (torch.randn(dm, di) / dm ** 0.5).bfloat16()
+        wu = (torch.randn(dm, di) / dm ** 0.5).bfloat16()
+        dout = torch.randn(bs, sq, di).bfloat16()
+        lo, hi = parallel.shard_bounds(di, rank, world)
+        wg_s = parallel.shard_columns(wg, rank, world).requires_grad_(True)
+        wu_s = parallel.shard_columns(wu, rank, world).requires_grad_(True)
+        out_s = parallel.ColumnParallelSwiGLU.apply(x, wg_s, wu_s, None, False, OracleBackend)
+        out_s.backward(dout[..., lo:hi].contiguous())
+        out_full = parallel.unshard_columns(out_s.detach())
+
+        xr = x.detach().clone().requires_grad_(True)
+        wgr = wg.clone().requires_grad_(True)
+        wur = wu.clone().requires_grad_(True)
+        ref = orc.swiglu_ref_torch(xr, wgr, wur)
+        ref.backward(dout)
+
+        def rel(a, b):
+            return (torch.linalg.norm(a.float() - b.float()) / torch.linalg.norm(b.float())).item()
+
+        errs = {
+            "out": rel(out_full, ref),
+            "dx": rel(x.grad, xr.grad),
+            "dwg": rel(wg_s.grad, wgr.grad[:, lo:hi]),
+            "dwu": rel(wu_s.grad, wur.grad[:, lo:hi]),
+        }
+        # every rank must hold the same reduced dX
+        gathered = [torch.empty_like(x.grad) for _ in range(world)]
+        dist.all_gather(gathered, x.grad)
+        errs["dx_equal_across_ranks"] = float(max((g.float() - gathered[0].float()).abs().max() for g in gathered))
+        q.put((rank, errs))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_column_parallel_matches_unsharded_reference():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, errs in results:
+        assert errs["dx_equal_across_ranks"] == 0.0, (rank, errs)
+        for k in ("out", "dx", "dwg", "dwu"):
+            assert errs[k] < 1e-2, (rank, k, errs)
+
+
+def test_shard_bounds_and_errors():
+    from fusedswiglu_b200 import parallel
+
+    assert parallel.shard_bounds(14336, 3, 8) == (5376, 7168)
+    assert [parallel.shard_bounds(28672, r, 4)[0] for r in range(4)] == [0, 7168, 14336, 21504]
+    with pytest.raises(ValueError, match="not divisible"):
+        parallel.shard_bounds(100, 0, 3)
+    with pytest.raises(ValueError, match="multiple of 8"):
+        parallel.shard_bounds(72, 0, 2)  # 36 columns per rank
+    with pytest.raises(ValueError, match="bad rank"):
+        parallel.shard_bounds(64, 2, 2)
+    w = torch.arange(4 * 32).view(4, 32)
+    s = parallel.shard_columns(w, 1, 2)
+    assert s.is_contiguous() and torch.equal(s, w[:, 16:])
+
+
+def _absent_rank_worker(rank, world, port, q):
+    import datetime
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    try:
+        if rank == 0:
+            try:
+                dist.all_reduce(torch.ones(4))
+                q.put("completed")
+            except Exception as e:  # the collective must end with an error, not hang
+                q.put("error:" + type(e).__name__)
+        else:
+            q.put("absent")  # this rank never joins the collective
+            import time
+
+            time.sleep(8)
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_rank_that_never_joins_ends_the_collective_with_an_error():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_absent_rank_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    msgs = sorted(q.get(timeout=60) for _ in range(world))
+    for p in procs:
+        p.join(timeout=30)
+    assert msgs[0] == "absent" and msgs[1].startswith("error:"), msgs
