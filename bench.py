@@ -1,0 +1,439 @@
+#!/usr/bin/env python
+"""Benchmark of the fused SwiGLU hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One "step" is one forward + backward pass of the SwiGLU MLP block over one batch
+of seeded synthetic tensors: the forward dual GEMM, the gate-gradient elementwise
+kernel, the dX GEMM and the dW dual GEMM (4 kernel launches of this library).
+FLOPs are counted as 2*M*N*K per GEMM, six GEMMs: 12*T*d_model*d_intermediate per
+step; elementwise work is not counted.
+
+With N > 1 (launched by torch.distributed.run, one rank per GPU) d_intermediate is
+sharded column-parallel: forward and dW are local, the partial dX is all-reduced
+with NCCL while the dW GEMM runs.  The total problem is fixed, so scaling is
+"strong".
+
+`--impl reference` times the reference path's PyTorch SwiGLU (forward + autograd
+backward) on the host CPU cores over a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+# name -> (bs, sq, d_model, d_intermediate, dtype)
+WORKLOADS = {
+    "llama3_8b_mlp": (8, 4096, 4096, 14336, "bf16"),
+    "readme": (4, 2048, 4096, 12288, "bf16"),
+    "llama3_70b_mlp": (16, 4096, 8192, 28672, "bf16"),
+    "plumbing": (1, 128, 512, 1536, "bf16"),
+}
+DEFAULT_WORKLOAD = "llama3_8b_mlp"
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+# DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum)
+# for the kernel named, on the workload named; see profiles/.  None = not captured.
+NCU_TRAFFIC_BYTES = {}
+
+CLOCK_QUERY = (
+    "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--only", default=None, choices=["fwd", "ew", "dx", "dw"],
+                    help="launch only this kernel in each step (for profiling one kernel); prints no bench line")
+    return ap.parse_args()
+
+
+def load_peaks():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    def __init__(self, gpu_id: str):
+        self.gpu_id = gpu_id
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        import tempfile
+
+        fd, self.path = tempfile.mkstemp(prefix="fsw_clocks_", suffix=".csv")
+        os.close(fd)
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", self.gpu_id],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL,
+            )
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = []
+        for line in Path(self.path).read_text().splitlines():
+            f = [s.strip() for s in line.split(",")]
+            if len(f) >= 9:
+                rows.append(f)
+        os.unlink(self.path)
+        if not rows:
+            return out
+        sm = sorted(float(r[1]) for r in rows if r[1].replace(".", "").isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[5 + i].lower().startswith("active") for r in rows)]
+        out.update(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=float(rows[0][2]) if rows[0][2] else None,
+                   reasons=reasons, samples=len(rows),
+                   power_w_max=max((float(r[3]) for r in rows if r[3].replace(".", "").isdigit()), default=None))
+        return out
+
+
+def flops_per_step(T, dm, di):
+    return 12.0 * T * dm * di
+
+
+# ------------------------------------------------------------ reference arm --
+def cpu_reference_run(bs, sq, dm, di, dtype, steps, warmup, sample_tokens, seed=0):
+    """The reference path's PyTorch SwiGLU + autograd on the host cores, over
+    `sample_tokens` tokens of the workload per step."""
+    import torch
+
+    from oracle import swiglu_oracle as orc
+
+    tdt = {"bf16": torch.bfloat16, "fp16": torch.float16}[dtype]
+    T = min(sample_tokens, bs * sq)
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(1, T, dm, generator=g).to(tdt).requires_grad_(True)
+    wg = (torch.randn(dm, di, generator=g) / dm ** 0.5).to(tdt).requires_grad_(True)
+    wu = (torch.randn(dm, di, generator=g) / dm ** 0.5).to(tdt).requires_grad_(True)
+    dout = torch.randn(1, T, di, generator=g).to(tdt)
+
+    def step():
+        x.grad = wg.grad = wu.grad = None
+        out = orc.swiglu_ref_torch(x, wg, wu)
+        out.backward(dout)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return {"tokens": T, "sec_per_step": dt, "tflops": flops_per_step(T, dm, di) / dt / 1e12,
+            "threads": torch.get_num_threads()}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+
+    bs, sq, dm, di, dtype = WORKLOADS[args.workload]
+    sample = 2048 if args.workload != "plumbing" else bs * sq
+    steps = max(1, min(args.steps, 5))
+    warmup = max(1, min(args.warmup, 1))
+    r = cpu_reference_run(bs, sq, dm, di, dtype, steps, warmup, sample, args.seed)
+    line = {
+        "impl": "reference",
+        "metric": "swiglu_fwd_bwd_tflops", "value": r["tflops"], "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": r["sec_per_step"] * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": {"workload": args.workload, "bs": bs, "sq": sq, "d_model": dm, "d_intermediate": di,
+                   "sample_tokens_per_step": r["tokens"], "device": "host CPU"},
+        "cpu_baseline": {"value": r["tflops"], "unit": "TFLOP/s", "cores": r["threads"], "kind": "port",
+                         "sample": f"{r['tokens']} of {bs * sq} tokens per step, {steps} steps, torch "
+                                   f"{torch.__version__} CPU, os.cpu_count()={os.cpu_count()}"},
+        "e2e": {"value": r["tflops"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "fwd_tokens_per_s": None,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ our arm --
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N>1 must be launched with torch.distributed.run (one rank per GPU)")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from fusedswiglu_b200 import FusedSwiGLU, _launch, _lib, parallel
+
+    _lib.load()
+    bs, sq, dm, di, dtype = WORKLOADS[args.workload]
+    tdt = {"bf16": torch.bfloat16, "fp16": torch.float16}[dtype]
+    T = bs * sq
+    lo, hi = parallel.shard_bounds(di, rank, world)
+    di_local = hi - lo
+    K, W = args.steps, max(args.warmup, 3)
+
+    # Seeded synthetic tensors; every rank draws the full tensors from one seed and
+    # keeps its column slice, so the sharded run computes the same problem.
+    g = torch.Generator(device=dev).manual_seed(args.seed)
+    x = torch.randn(bs, sq, dm, device=dev, dtype=tdt, generator=g)
+    wg_full = torch.randn(dm, di, device=dev, dtype=tdt, generator=g) / dm ** 0.5
+    wu_full = torch.randn(dm, di, device=dev, dtype=tdt, generator=g) / dm ** 0.5
+    wg = wg_full[:, lo:hi].contiguous()
+    wu = wu_full[:, lo:hi].contiguous()
+    del wg_full, wu_full
+    dout = torch.randn(bs, sq, di_local, device=dev, dtype=tdt, generator=g)
+    x2d = x.view(T, dm)
+    dout2d = dout.view(T, di_local)
+
+    names = ["fwd_dual_gemm", "gate_grad_elementwise", "dx_gemm", "dw_dual_gemm"]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(K)]
+
+    def step(marks=None):
+        if marks: marks[0].record()
+        out, gg, uu = _launch.forward(x2d, wg, wu)
+        if marks: marks[1].record()
+        dg, du = _launch.gate_grad(dout2d, gg, uu)
+        if marks: marks[2].record()
+        dx = _launch.grad_input(dg, du, wg, wu)
+        if marks: marks[3].record()
+        work = dist.all_reduce(dx, async_op=True) if world > 1 else None
+        dwg, dwu = _launch.grad_weights(x2d, dg, du)
+        if marks: marks[4].record()
+        if work is not None:
+            work.wait()
+        return out, dx, dwg, dwu
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if args.only:
+        # Profiling aid: the other kernels run once to produce this kernel's inputs.
+        out, gg, uu = _launch.forward(x2d, wg, wu)
+        dg, du = _launch.gate_grad(dout2d, gg, uu)
+        one = {
+            "fwd": lambda: _launch.forward(x2d, wg, wu),
+            "ew": lambda: _launch.gate_grad(dout2d, gg, uu),
+            "dx": lambda: _launch.grad_input(dg, du, wg, wu),
+            "dw": lambda: _launch.grad_weights(x2d, dg, du),
+        }[args.only]
+        for _ in range(W):
+            one()
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(K):
+            one()
+        t1.record()
+        barrier()
+        ms = t0.elapsed_time(t1) / K
+        print(json.dumps({"only": args.only, "workload": args.workload, "ms": ms, "steps": K,
+                          "tflops": (4.0 * T * dm * di_local / ms / 1e9) if args.only != "ew" else None,
+                          "status": _lib.device_status()}), flush=True)
+        return
+
+    for _ in range(W):
+        step()
+    barrier()
+    props = torch.cuda.get_device_properties(dev)
+    gpu_id = str(getattr(props, "uuid", local_rank))
+    if not gpu_id.startswith("GPU-") and len(gpu_id) > 8:
+        gpu_id = "GPU-" + gpu_id
+    sampler = ClockSampler(gpu_id if rank == 0 else str(local_rank))
+    if rank == 0:
+        sampler.start()
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_start.record()
+    for i in range(K):
+        step(ev[i])
+    t_end.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t_start.elapsed_time(t_end)
+    per_kernel_ms = [sum(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(K)) / K for j in range(4)]
+    if world > 1:
+        tt = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        total_ms = float(tt.item())
+    status = _lib.device_status()
+    if status != 0:
+        raise SystemExit(f"a kernel gave up on a bounded wait (status {status}); no number reported")
+    ms_per_step = total_ms / K
+    total_flops = flops_per_step(T, dm, di)  # whole job, all ranks
+    value = total_flops / ms_per_step / 1e9
+
+    # ---- end to end through the public autograd API with host buffers
+    e2e = None
+    if not args.no_e2e:
+        hx = torch.empty_like(x, device="cpu").pin_memory()
+        hdout = torch.empty_like(dout, device="cpu").pin_memory()
+        hx.copy_(x)
+        hdout.copy_(dout)
+        hdx = torch.empty_like(x, device="cpu").pin_memory()
+        wgp = wg.clone().requires_grad_(True)
+        wup = wu.clone().requires_grad_(True)
+        copy_stream = torch.cuda.Stream(device=dev)
+        dx_dev = torch.empty_like(x)
+        dout_dev = torch.empty_like(dout)
+        x_dev = torch.empty_like(x)
+
+        def e2e_step():
+            main = torch.cuda.current_stream(dev)
+            copy_stream.wait_stream(main)
+            with torch.cuda.stream(copy_stream):
+                x_dev.copy_(hx, non_blocking=True)
+                ex = torch.cuda.Event(); ex.record()
+                dout_dev.copy_(hdout, non_blocking=True)
+                ed = torch.cuda.Event(); ed.record()
+            main.wait_event(ex)
+            xin = x_dev.detach().requires_grad_(True)
+            wgp.grad = wup.grad = None
+            if world > 1:
+                out = parallel.column_parallel_swiglu(xin, wgp, wup)
+            else:
+                out = FusedSwiGLU.apply(xin, wgp, wup)
+            main.wait_event(ed)
+            out.backward(dout_dev)
+            hdx.copy_(xin.grad, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        n_e2e = max(3, min(K, 10))
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        s1.record()
+        barrier()
+        e2e_ms = s0.elapsed_time(s1) / n_e2e
+        if world > 1:
+            tt = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            e2e_ms = float(tt.item())
+        e2e = {"value": total_flops / e2e_ms / 1e9, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": hx.numel() * 2 + hdout.numel() * 2, "d2h_bytes_per_step": hdx.numel() * 2,
+               "ms_per_step": e2e_ms, "steps": n_e2e,
+               "api": "FusedSwiGLU.apply + backward" if world == 1 else "ColumnParallelSwiGLU.apply + backward",
+               "note": "x and dout copied from pinned host memory and dX copied back every step; weights stay resident"}
+        status = _lib.device_status()
+        if status != 0:
+            raise SystemExit(f"a kernel gave up on a bounded wait (status {status}) in the end-to-end loop")
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_src = load_peaks()
+    gemm_flops_local = 4.0 * T * dm * di_local
+    kern = {}
+    for j, n in enumerate(names):
+        ms = per_kernel_ms[j]
+        if n == "gate_grad_elementwise":
+            gbs = 5.0 * T * di_local * 2 / ms / 1e6
+            kern[n] = {"ms": ms, "achieved": gbs, "unit": "GB/s", "bound": "hbm", "frac": gbs / peaks["hbm_gbs"]}
+        else:
+            tf = gemm_flops_local / ms / 1e9
+            kern[n] = {"ms": ms, "achieved": tf, "unit": "TFLOP/s", "bound": "tensor",
+                       "frac": tf / peaks["bf16_tflops_sustained"]}
+    dom = max((n for n in names if n != "gate_grad_elementwise"), key=lambda n: kern[n]["ms"])
+    roofline = {
+        "kernel": dom, "bound": "tensor", "achieved": kern[dom]["achieved"], "peak": peaks["bf16_tflops_sustained"],
+        "unit": "TFLOP/s", "frac": kern[dom]["achieved"] / peaks["bf16_tflops_sustained"],
+        "peak_source": f"{peak_src} bf16_tflops_sustained (kernel timed inside a long step)",
+        "frac_of_burst": kern[dom]["achieved"] / peaks["bf16_tflops"],
+        "frac_of_nominal": kern[dom]["achieved"] / NOMINAL_BF16_TFLOPS,
+        "algorithmic_flops_per_launch": gemm_flops_local,
+        "traffic": NCU_TRAFFIC_BYTES.get((dom, args.workload, world)),
+        "kernels": kern,
+    }
+    fwd_tokens_per_s = T / (per_kernel_ms[0] / 1e3)
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        r = cpu_reference_run(bs, sq, dm, di, dtype, steps=3, warmup=1,
+                              sample_tokens=2048 if args.workload != "plumbing" else T, seed=args.seed)
+        cpu_baseline = {"value": r["tflops"], "unit": "TFLOP/s", "cores": r["threads"], "kind": "port",
+                        "sample": f"{r['tokens']} of {T} tokens per step, 3 steps after 1 warm-up, "
+                                  f"PyTorch SwiGLU + autograd on CPU, os.cpu_count()={os.cpu_count()}"}
+
+    line = {
+        "metric": "swiglu_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": {"workload": args.workload, "bs": bs, "sq": sq, "d_model": dm, "d_intermediate": di,
+                   "parallelism": f"column-parallel d_intermediate x{world}" if world > 1 else "single GPU",
+                   "l2": "inputs larger than L2 (activations and weights exceed 126 MB); no flush",
+                   "accumulate": "fp32", "cta_group": _lib.get_option("cta_group"),
+                   "group_m": _lib.get_option("group_m")},
+        "frac_of_nominal_bf16_peak": value / (NOMINAL_BF16_TFLOPS * world),
+        "frac_of_measured_sustained": value / (peaks["bf16_tflops_sustained"] * world),
+        "fwd_tokens_per_s": fwd_tokens_per_s,
+        "gpu_launches": 4 * K,
+        "clocks": clocks,
+        "roofline": roofline,
+        "e2e": e2e,
+        "cpu_baseline": cpu_baseline,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

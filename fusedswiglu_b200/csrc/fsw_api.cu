@@ -425,6 +425,14 @@ int64_t fsw_get_option(const char* name) {
   if (!strcmp(name, "mn_lbo")) return g_opt.mn_lbo;
   if (!strcmp(name, "mn_sbo")) return g_opt.mn_sbo;
   if (!strcmp(name, "mn_kadv")) return g_opt.mn_kadv;
+  if (!strcmp(name, "max_pairs") || !strcmp(name, "sm_count") || !strcmp(name, "stages")) {
+    // facts about the current device (initialises it on first use)
+    DeviceInfo* d = nullptr;
+    if (ensure_device(&d) != FSW_OK) return -1;
+    if (!strcmp(name, "max_pairs")) return d->max_pairs;
+    if (!strcmp(name, "sm_count")) return d->sm_count;
+    return g_opt.cta_group == 2 ? TileCfg<MODE_FWD, 2>::STAGES : TileCfg<MODE_FWD, 1>::STAGES;
+  }
   return -1;
 }
 
@@ -432,6 +440,7 @@ int fsw_forward(const void* x, const void* w_gate, const void* w_up, void* out, 
                 int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream) {
   int rc = check_common(T, dm, di, dtype, accum);
   if (rc != FSW_OK) return rc;
+  if (T == 0) return FSW_OK;  // nothing to compute; empty tensors may have NULL storage
   if (!x || !w_gate || !w_up || !out) return fail(FSW_EINVAL, "x, w_gate, w_up and out are required");
   if ((g == nullptr) != (u == nullptr))
     return fail(FSW_EINVAL, "g and u must both be given or both be NULL");
@@ -440,8 +449,6 @@ int fsw_forward(const void* x, const void* w_gate, const void* w_up, void* out, 
     return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
   DeviceInfo* d = nullptr;
   if ((rc = ensure_device(&d)) != FSW_OK) return rc;
-  if (T == 0) return FSW_OK;
-  const int cg = (int)g_opt.cta_group;
   GemmParams p;
   memset(&p, 0, sizeof(p));
   if ((rc = make_map(&p.a0, x, dtype, dm, T, 128, "x")) != FSW_OK) return rc;
@@ -451,11 +458,13 @@ int fsw_forward(const void* x, const void* w_gate, const void* w_up, void* out, 
   if ((rc = make_map(&p.c0, g ? g : out, dtype, di, T, 32, "g")) != FSW_OK) return rc;
   if ((rc = make_map(&p.c1, u ? u : out, dtype, di, T, 32, "u")) != FSW_OK) return rc;
   if ((rc = make_map(&p.c2, out, dtype, di, T, 32, "out")) != FSW_OK) return rc;
-  (void)cg;
   p.M = (int)T;
   p.N = (int)di;
   p.num_k_blocks = (int)((dm + 63) / 64);
   p.store_gu = g != nullptr;
+  p.c0_ptr = g;
+  p.c1_ptr = u;
+  p.c2_ptr = out;
   return run_gemm<MODE_FWD>(p, (int)T, dtype, accum == FSW_ACC_F16,
                             static_cast<cudaStream_t>(stream), d);
 }
@@ -494,12 +503,12 @@ int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const vo
                     int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream) {
   int rc = check_common(T, dm, di, dtype, accum);
   if (rc != FSW_OK) return rc;
+  if (T == 0) return FSW_OK;
   if (!dg || !du || !w_gate || !w_up || !dx) return fail(FSW_EINVAL, "NULL pointer");
   if (!aligned16(dg) || !aligned16(du) || !aligned16(w_gate) || !aligned16(w_up) || !aligned16(dx))
     return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
   DeviceInfo* d = nullptr;
   if ((rc = ensure_device(&d)) != FSW_OK) return rc;
-  if (T == 0) return FSW_OK;
   const int cg = (int)g_opt.cta_group;
   GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -510,6 +519,7 @@ int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const vo
   if ((rc = make_map(&p.c0, dx, dtype, dm, T, 32, "dx")) != FSW_OK) return rc;
   p.c1 = p.c0;
   p.c2 = p.c0;
+  p.c0_ptr = dx;
   p.M = (int)T;
   p.N = (int)dm;
   p.num_k_blocks = (int)((di + 63) / 64);
@@ -543,6 +553,8 @@ int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate
   if ((rc = make_map(&p.c0, dw_gate, dtype, di, dm, 32, "dw_gate")) != FSW_OK) return rc;
   if ((rc = make_map(&p.c1, dw_up, dtype, di, dm, 32, "dw_up")) != FSW_OK) return rc;
   p.c2 = p.c0;
+  p.c0_ptr = dw_gate;
+  p.c1_ptr = dw_up;
   p.M = (int)dm;
   p.N = (int)di;
   p.num_k_blocks = (int)((T + 63) / 64);

@@ -53,7 +53,16 @@ struct GemmParams {
   int num_k_blocks;        // 64-wide K blocks per product
   int store_gu;            // MODE_FWD: also write g and u
   uint32_t* status;        // device status word (0 = ok)
+  void *c0_ptr, *c1_ptr, *c2_ptr;  // raw output pointers (direct-store epilogue)
 };
+
+// Epilogue store path: 0 = stage 32x64 boxes in swizzled shared memory and let TMA
+// write them; 1 = 16-byte global stores straight from registers, which frees the
+// staging space for more operand stages.
+#ifndef FSW_EPI_DIRECT
+#define FSW_EPI_DIRECT 0
+#endif
+constexpr int kSmemBudget = 232448;  // 227 KB opt-in limit per CTA
 
 template <int MODE, int CG>
 struct TileCfg {
@@ -66,13 +75,15 @@ struct TileCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = B_ROWS * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (CG == 1) ? 3 : 5;
   static constexpr int CHUNK_BYTES = 64 * BK * 2;  // one MN-major 64x64 box
+  static constexpr bool EPI_DIRECT = FSW_EPI_DIRECT != 0;
   static constexpr int EPI_WARPS = 4;
   static constexpr int EPI_NBUF = 3;
   static constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows x 64 16-bit columns
-  static constexpr int EPI_BYTES = EPI_WARPS * EPI_NBUF * EPI_BUF_BYTES;
+  static constexpr int EPI_BYTES = EPI_DIRECT ? 0 : EPI_WARPS * EPI_NBUF * EPI_BUF_BYTES;
   static constexpr int BAR_BYTES = 256;
+  // as many operand stages as fit beside the epilogue staging
+  static constexpr int STAGES = (kSmemBudget - 1024 - BAR_BYTES - EPI_BYTES) / STAGE_BYTES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;
   static constexpr int THREADS = 192;
   static constexpr int TMEM_COLS = 512;
@@ -365,7 +376,7 @@ __global__ void __launch_bounds__(192, 1) gemm_kernel(const __grid_constant__ Ge
             ptx::tmem_ld_32x32(taddr + 128 + jb * 64 + h * 32, ru);
             ptx::tmem_ld_wait();
             if (jb == 1 && h == 1) release_tmem();
-            if (h == 0) {
+            if (!C::EPI_DIRECT && h == 0) {
               if (lane == 0) ptx::tma_store_wait_read<0>();
               __syncwarp();
             }
@@ -398,12 +409,26 @@ __global__ void __launch_bounds__(192, 1) gemm_kernel(const __grid_constant__ Ge
                   po[e] = pack2<T>(u0 * s0, u1 * s1);
                 }
               }
-              const uint32_t off = row_off + (((h * 4 + i) ^ sw) << 4);
-              ptx::st_shared_v4(buf_g + off, pg[0], pg[1], pg[2], pg[3]);
-              ptx::st_shared_v4(buf_u + off, pu[0], pu[1], pu[2], pu[3]);
-              ptx::st_shared_v4(buf_o + off, po[0], po[1], po[2], po[3]);
+              if (C::EPI_DIRECT) {
+                const int row = row0 + lane;
+                const int col = n0 + jb * 64 + h * 32 + i * 8;
+                if (row < p.M && col < p.N) {
+                  const size_t off = (static_cast<size_t>(row) * p.N + col) * 2;
+                  if (p.store_gu) {
+                    ptx::st_global_v4(static_cast<char*>(p.c0_ptr) + off, pg[0], pg[1], pg[2], pg[3]);
+                    ptx::st_global_v4(static_cast<char*>(p.c1_ptr) + off, pu[0], pu[1], pu[2], pu[3]);
+                  }
+                  ptx::st_global_v4(static_cast<char*>(p.c2_ptr) + off, po[0], po[1], po[2], po[3]);
+                }
+              } else {
+                const uint32_t off = row_off + (((h * 4 + i) ^ sw) << 4);
+                ptx::st_shared_v4(buf_g + off, pg[0], pg[1], pg[2], pg[3]);
+                ptx::st_shared_v4(buf_u + off, pu[0], pu[1], pu[2], pu[3]);
+                ptx::st_shared_v4(buf_o + off, po[0], po[1], po[2], po[3]);
+              }
             }
           }
+          if (C::EPI_DIRECT) continue;
           ptx::fence_proxy_async_smem();
           __syncwarp();
           const int col = n0 + jb * 64;
@@ -424,9 +449,12 @@ __global__ void __launch_bounds__(192, 1) gemm_kernel(const __grid_constant__ Ge
           ptx::tmem_ld_32x32(taddr + jb * 64 + 32, r1);
           ptx::tmem_ld_wait();
           if (jb == 3) release_tmem();
-          if (lane == 0) ptx::tma_store_wait_read<C::EPI_NBUF - 1>();
-          __syncwarp();
+          if (!C::EPI_DIRECT) {
+            if (lane == 0) ptx::tma_store_wait_read<C::EPI_NBUF - 1>();
+            __syncwarp();
+          }
           const uint32_t buf = my_epi + rb * C::EPI_BUF_BYTES;
+          const int col = (MODE == MODE_DX) ? (n0 + jb * 64) : (n0 + (jb & 1) * 64);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             uint32_t pk[4];
@@ -440,11 +468,21 @@ __global__ void __launch_bounds__(192, 1) gemm_kernel(const __grid_constant__ Ge
               else
                 pk[e] = pack2<T>(__uint_as_float(v0), __uint_as_float(v1));
             }
-            ptx::st_shared_v4(buf + row_off + ((i ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
+            if (C::EPI_DIRECT) {
+              const int row = row0 + lane;
+              const int cc = col + i * 8;
+              if (row < p.M && cc < p.N) {
+                char* base = static_cast<char*>((MODE == MODE_DW && jb >= 2) ? p.c1_ptr : p.c0_ptr);
+                ptx::st_global_v4(base + (static_cast<size_t>(row) * p.N + cc) * 2, pk[0], pk[1], pk[2],
+                                  pk[3]);
+              }
+            } else {
+              ptx::st_shared_v4(buf + row_off + ((i ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
+            }
           }
+          if (C::EPI_DIRECT) continue;
           ptx::fence_proxy_async_smem();
           __syncwarp();
-          const int col = (MODE == MODE_DX) ? (n0 + jb * 64) : (n0 + (jb & 1) * 64);
           if (lane == 0) {
             if (row0 < p.M && col < p.N)
               ptx::tma_store_2d((MODE == MODE_DW && jb >= 2) ? &p.c1 : &p.c0, buf, col, row0);

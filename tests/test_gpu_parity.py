@@ -1,0 +1,408 @@
+"""Parity of the CUDA path (called through the C ABI) with the CPU oracle, the
+golden vectors of the reference's own PyTorch SwiGLU, and the reference's own
+test recipe.  Everything here needs a B200."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN_CASES, load_golden
+from oracle import swiglu_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+# The reference's bound on ||a-b||_F/||b||_F for out, dX, dW_gate, dW_up
+# (fused_swiglu/test_swiglu.py:20) and the level it says to expect.
+BFLOAT16_MAX_TOL = 1e-2
+EXPECTED_BF16 = 6e-3
+EXPECTED_FP16 = 1e-3
+
+TDT = {"bf16": torch.bfloat16, "fp16": torch.float16}
+
+
+@pytest.fixture(scope="module", autouse=True)
+def cuda_ready():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from fusedswiglu_b200 import _lib
+
+    _lib.load()
+    yield
+    assert _lib.device_status() == 0, "a kernel gave up on a bounded wait"
+
+
+def dev(a, dtype):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(TDT[dtype]).cuda()
+
+
+def host(t):
+    return t.detach().float().cpu().numpy()
+
+
+def run_cuda(inp, dtype, fast_accum=False):
+    """Forward + backward through the package's launchers (ctypes -> C ABI)."""
+    from fusedswiglu_b200 import _launch
+
+    bs, sq, dm = inp["x"].shape
+    di = inp["w_gate"].shape[1]
+    x = dev(inp["x"].reshape(bs * sq, dm), dtype)
+    wg, wu = dev(inp["w_gate"], dtype), dev(inp["w_up"], dtype)
+    dout = dev(inp["dout"].reshape(bs * sq, di), dtype)
+    out, g, u = _launch.forward(x, wg, wu, fast_accum=fast_accum)
+    dg, du = _launch.gate_grad(dout, g, u)
+    dx = _launch.grad_input(dg, du, wg, wu)
+    dwg, dwu = _launch.grad_weights(x, dg, du, fast_accum=fast_accum)
+    torch.cuda.synchronize()
+    return {
+        "out": host(out).reshape(bs, sq, di), "g": host(g).reshape(bs, sq, di), "u": host(u).reshape(bs, sq, di),
+        "dg": host(dg).reshape(bs, sq, di), "du": host(du).reshape(bs, sq, di),
+        "dx": host(dx).reshape(bs, sq, dm), "dw_gate": host(dwg), "dw_up": host(dwu),
+    }
+
+
+# --------------------------------------------------------- golden fixtures --
+@pytest.mark.parametrize("cta_group", [1, 2])
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_against_reference_golden(name, cta_group):
+    from fusedswiglu_b200 import _lib
+
+    c = load_golden(name)
+    _lib.set_option("cta_group", cta_group)
+    try:
+        got = run_cuda(c, c["dtype"])
+    finally:
+        _lib.set_option("cta_group", 2)
+    step = c["row_step"]
+    got["dw_gate"], got["dw_up"] = got["dw_gate"][::step], got["dw_up"][::step]
+    expected = EXPECTED_BF16 if c["dtype"] == "bf16" else EXPECTED_FP16
+    for k in ("out", "dx", "dw_gate", "dw_up"):
+        rep = orc.error_report(got[k], c[k])
+        print(name, cta_group, k, rep)
+        assert rep["rel_fro"] < BFLOAT16_MAX_TOL, (name, k, rep)
+        assert rep["rel_fro"] < expected, (name, k, rep)
+
+
+# ------------------------------------------ oracle, kernel rounding order --
+RAGGED = [64, 128, 192, 320]
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("T", RAGGED)
+def test_ragged_shapes_against_kernel_order_oracle(T, dtype):
+    worst = {}
+    for dm in RAGGED:
+        for di in RAGGED:
+            inp = orc.make_inputs(1, T, dm, di, dtype, seed=T + dm + di, dout_std=0.5)
+            got = run_cuda(inp, dtype)
+            out, g, u = orc.kernel_forward(inp["x"], inp["w_gate"], inp["w_up"], dtype)
+            # the elementwise step is checked on the GPU's own g, u so that one-ulp
+            # differences in g do not blur it
+            du, dg = orc.kernel_elementwise_backward(inp["dout"], got["g"], got["u"], dtype)
+            dx64 = got["dg"].reshape(T, di).astype(np.float64) @ inp["w_gate"].T.astype(np.float64) + \
+                got["du"].reshape(T, di).astype(np.float64) @ inp["w_up"].T.astype(np.float64)
+            dwg64 = inp["x"].reshape(T, dm).T.astype(np.float64) @ got["dg"].reshape(T, di).astype(np.float64)
+            dwu64 = inp["x"].reshape(T, dm).T.astype(np.float64) @ got["du"].reshape(T, di).astype(np.float64)
+            want = {"out": out, "g": g, "u": u, "dg": dg, "du": du,
+                    "dx": orc.round16(dx64.astype(np.float32), dtype).reshape(1, T, dm),
+                    "dw_gate": orc.round16(dwg64.astype(np.float32), dtype),
+                    "dw_up": orc.round16(dwu64.astype(np.float32), dtype)}
+            for k, w in want.items():
+                e = orc.rel_error(got[k], w)
+                worst[k] = max(worst.get(k, 0.0), e)
+                # same rounding points as the oracle: only ulp-level flips remain
+                assert e < 1e-3, (T, dm, di, k, e)
+                mism = np.mean(orc.to_bits(got[k], dtype) != orc.to_bits(w, dtype))
+                assert mism < 0.03, (T, dm, di, k, mism)
+    print("worst rel error per tensor:", worst)
+
+
+def test_gemm_outputs_are_bit_exact_against_wide_accumulation():
+    """g, u, dX, dW are pure GEMMs with fp32 accumulation and one rounding: except
+    for sums that land within an fp32 rounding of a bf16 tie, the bits must equal a
+    float64-accumulated result."""
+    inp = orc.make_inputs(2, 128, 256, 384, "bf16", seed=11, dout_std=0.5)
+    got = run_cuda(inp, "bf16")
+    _, g, u = orc.kernel_forward(inp["x"], inp["w_gate"], inp["w_up"], "bf16")
+    for k, w in (("g", g), ("u", u)):
+        mism = np.mean(orc.to_bits(got[k], "bf16") != orc.to_bits(w, "bf16"))
+        assert mism < 2e-3, (k, mism)
+
+
+# ----------------------------------------------- the reference's own tests --
+def _ref_shapes():
+    num = int(os.environ.get("NUM_TEST", "3"))
+    return orc.reference_test_shapes(num)
+
+
+def make_input_weights(bs, sq, d_model, d_intermediate, dtype=torch.bfloat16):
+    # test_swiglu.py:23-40: randn in the 16-bit dtype, weights divided by sqrt(d_model)
+    x = torch.randn((bs, sq, d_model), device="cuda:0", dtype=dtype).requires_grad_(True)
+    w_gate = torch.randn((d_model, d_intermediate), device="cuda:0", dtype=dtype) / math.sqrt(d_model)
+    w_up = torch.randn((d_model, d_intermediate), device="cuda:0", dtype=dtype) / math.sqrt(d_model)
+    return x, w_gate.requires_grad_(True), w_up.requires_grad_(True)
+
+
+def rel_error(x, y):
+    return (torch.linalg.norm(x.float() - y.float()) / torch.linalg.norm(y.float())).item()
+
+
+def test_reference_forward_suite():
+    """test_swiglu_fwd (test_swiglu.py:58-78) over its 81 seeded shapes."""
+    from fused_swiglu import FusedSwiGLU
+
+    torch.manual_seed(0)
+    worst = 0.0
+    for dims in _ref_shapes()[0]:
+        x, wg, wu = make_input_weights(*dims)
+        with torch.no_grad():
+            ref = orc.swiglu_ref_torch(x, wg, wu)
+            out = FusedSwiGLU.apply(x, wg, wu)
+        e = rel_error(out, ref)
+        worst = max(worst, e)
+        assert e < BFLOAT16_MAX_TOL, (dims, e)
+    print("worst forward rel error over the reference's shapes:", worst)
+    assert worst < EXPECTED_BF16
+
+
+def test_reference_backward_suite():
+    """test_swiglu_bwd (test_swiglu.py:81-114) over its 81 seeded shapes."""
+    from fused_swiglu import FusedSwiGLU
+
+    torch.manual_seed(0)
+    worst = {}
+    for dims in _ref_shapes()[1]:
+        x, wg, wu = make_input_weights(*dims)
+        ref = orc.swiglu_ref_torch(x, wg, wu)
+        dy = 0.1 * torch.randn_like(ref)
+        ref.backward(dy, retain_graph=True)
+        want = [t.grad.clone() for t in (x, wg, wu)]
+        x.grad, wg.grad, wu.grad = None, None, None
+        out = FusedSwiGLU.apply(x, wg, wu)
+        out.backward(dy, retain_graph=True)
+        got = [t.grad.clone() for t in (x, wg, wu)]
+        for name, a, b in zip(("dx", "dw_gate", "dw_up"), got, want):
+            assert a.shape == b.shape
+            e = rel_error(a, b)
+            worst[name] = max(worst.get(name, 0.0), e)
+            assert e < BFLOAT16_MAX_TOL, (dims, name, e)
+    print("worst backward rel errors over the reference's shapes:", worst)
+    assert max(worst.values()) < EXPECTED_BF16
+
+
+# ------------------------------------------------------------- fp16 paths --
+@pytest.mark.parametrize("d_model", [1024, 2048])
+def test_fp16_fast_accum_against_fp32_accum(d_model):
+    """The fp16-accumulator variant is compared with the fp32-accumulate result,
+    which the oracle pins; errors are reported per tensor."""
+    bs, sq, di = 2, 512, 3 * d_model
+    inp = orc.make_inputs(bs, sq, d_model, di, "fp16", seed=2, dout_std=0.1)
+    slow = run_cuda(inp, "fp16", fast_accum=False)
+    fast = run_cuda(inp, "fp16", fast_accum=True)
+    for k in ("out", "dx", "dw_gate", "dw_up"):
+        rep = orc.error_report(fast[k], slow[k])
+        print(d_model, k, rep)
+        assert np.all(np.isfinite(fast[k]))
+        assert rep["rel_fro"] < BFLOAT16_MAX_TOL, (k, rep)
+
+
+def test_fast_accum_function_matches_reference_semantics():
+    from fused_swiglu import FastAccumFusedSwiGLU
+    from fused_swiglu.kernels.kernels_fp16 import fused_swiglu_fwd
+
+    torch.manual_seed(1)
+    x, wg, wu = make_input_weights(2, 256, 512, 1024, dtype=torch.float16)
+    ref = orc.swiglu_ref_torch(x, wg, wu)
+    dy = 0.1 * torch.randn_like(ref)
+    ref.backward(dy)
+    want = [t.grad.clone() for t in (x, wg, wu)]
+    x.grad, wg.grad, wu.grad = None, None, None
+    out = FastAccumFusedSwiGLU.apply(x, wg, wu)
+    out.backward(dy)
+    assert rel_error(out, ref) < BFLOAT16_MAX_TOL
+    for a, b in zip((x.grad, wg.grad, wu.grad), want):
+        assert rel_error(a, b) < BFLOAT16_MAX_TOL
+    o32, g32, u32 = fused_swiglu_fwd(x.detach(), wg.detach(), wu.detach(), fast_accum=False)
+    assert rel_error(o32, ref) < EXPECTED_FP16
+    assert rel_error(g32, x.detach() @ wg.detach()) < EXPECTED_FP16
+
+
+# --------------------------------------------------- API surface behaviour --
+def test_module_level_launchers_and_return_orders():
+    from fused_swiglu.kernels.kernels_bf16 import elementwise_backward, fused_bmm, fused_swiglu_fwd
+
+    torch.manual_seed(2)
+    x, wg, wu = make_input_weights(3, 128, 192, 320)
+    x, wg, wu = x.detach(), wg.detach(), wu.detach()
+    out, g, u = fused_swiglu_fwd(x, wg, wu)
+    assert out.shape == g.shape == u.shape == (3, 128, 320)
+    assert rel_error(g, x @ wg) < EXPECTED_BF16 and rel_error(u, x @ wu) < EXPECTED_BF16
+    dy = torch.randn_like(out)
+    d_up, d_gate = elementwise_backward(dy, g, u)  # up first, like the reference
+    gf = g.float()
+    s = torch.sigmoid(gf)
+    assert rel_error(d_up, dy.float() * gf * s) < 6e-3
+    assert rel_error(d_gate, dy.float() * u.float() * (s + gf * s * (1 - s))) < 6e-3
+    xT = x.transpose(1, 2)  # (bs, d_model, sq) strided view, as swiglu.py:51 passes
+    gw_up, gw_gate = fused_bmm(xT, d_up, d_gate)
+    assert gw_up.shape == (3, 192, 320)
+    assert rel_error(gw_up, torch.bmm(xT.float(), d_up.float())) < EXPECTED_BF16
+    assert rel_error(gw_gate, torch.bmm(xT.float(), d_gate.float())) < EXPECTED_BF16
+
+
+def test_autocast_inputs_are_cast_like_custom_fwd():
+    from fused_swiglu import FusedSwiGLU
+
+    torch.manual_seed(3)
+    x = torch.randn(1, 64, 128, device="cuda")
+    wg = torch.randn(128, 256, device="cuda") / 11
+    wu = torch.randn(128, 256, device="cuda") / 11
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = FusedSwiGLU.apply(x, wg, wu)
+    assert out.dtype == torch.bfloat16
+    ref = orc.swiglu_ref_torch(x.bfloat16(), wg.bfloat16(), wu.bfloat16())
+    assert rel_error(out, ref) < EXPECTED_BF16
+
+
+def test_non_contiguous_inputs_and_needs_input_grad():
+    from fused_swiglu import FusedSwiGLU
+
+    torch.manual_seed(4)
+    xb = torch.randn(2, 64, 256, device="cuda", dtype=torch.bfloat16)
+    x = xb[:, :, ::2].requires_grad_(False)  # strided, no grad
+    wg = (torch.randn(128, 192, device="cuda", dtype=torch.bfloat16) / 11).requires_grad_(True)
+    wu = (torch.randn(192, 128, device="cuda", dtype=torch.bfloat16) / 11).t().requires_grad_(True)  # strided
+    out = FusedSwiGLU.apply(x, wg, wu)
+    ref = orc.swiglu_ref_torch(x, wg.detach(), wu.detach())
+    assert rel_error(out, ref) < EXPECTED_BF16
+    out.sum().backward()
+    assert wg.grad is not None and wg.grad.shape == wg.shape
+
+
+# ------------------------------------------------------------- edge cases --
+def _canary(shape, dtype, rows_pad=4):
+    """Output buffer with guard rows before and after, filled with a sentinel."""
+    full = torch.full((shape[0] + 2 * rows_pad, shape[1]), 777.0, device="cuda", dtype=dtype)
+    return full, full[rows_pad:rows_pad + shape[0]]
+
+
+@pytest.mark.parametrize("T,dm,di", [(1, 64, 64), (100, 72, 136), (257, 200, 520), (130, 8, 8), (64, 1032, 24)])
+def test_edge_shapes_through_the_c_abi_with_guard_rows(T, dm, di):
+    """Tokens not a multiple of any tile, feature sizes that are only multiples of
+    8, and guard rows around every output to catch out-of-bounds stores."""
+    from fusedswiglu_b200 import _lib
+
+    lib = _lib.load()
+    inp = orc.make_inputs(1, T, dm, di, "bf16", seed=T, dout_std=0.5)
+    x, wg, wu = dev(inp["x"][0], "bf16"), dev(inp["w_gate"], "bf16"), dev(inp["w_up"], "bf16")
+    dout = dev(inp["dout"][0], "bf16")
+    bufs = {k: _canary(s, torch.bfloat16) for k, s in
+            {"out": (T, di), "g": (T, di), "u": (T, di), "dg": (T, di), "du": (T, di), "dx": (T, dm),
+             "dwg": (dm, di), "dwu": (dm, di)}.items()}
+    v = {k: b[1] for k, b in bufs.items()}
+    st = torch.cuda.current_stream().cuda_stream
+    p = lambda t: t.data_ptr()
+    _lib.check("fwd", lib.fsw_forward(p(x), p(wg), p(wu), p(v["out"]), p(v["g"]), p(v["u"]), T, dm, di, 0, 0, st))
+    _lib.check("bwd", lib.fsw_backward(p(dout), p(x), p(wg), p(wu), p(v["g"]), p(v["u"]), p(v["dg"]), p(v["du"]),
+                                       p(v["dx"]), p(v["dwg"]), p(v["dwu"]), T, dm, di, 0, 0, st))
+    torch.cuda.synchronize()
+    for k, (full, view) in bufs.items():
+        assert torch.all(full[:4] == 777.0) and torch.all(full[-4:] == 777.0), f"{k}: guard rows overwritten"
+        assert not torch.any(view == 777.0), f"{k}: elements left unwritten"
+    out, g, u = orc.kernel_forward(inp["x"], inp["w_gate"], inp["w_up"], "bf16")
+    dxr, dwgr, dwur = orc.swiglu_ref_backward(inp["x"], inp["w_gate"], inp["w_up"], inp["dout"], "bf16")
+    assert orc.rel_error(host(v["out"]), out[0]) < 1e-3
+    assert orc.rel_error(host(v["dx"]), dxr[0]) < EXPECTED_BF16
+    assert orc.rel_error(host(v["dwg"]), dwgr) < EXPECTED_BF16
+    assert orc.rel_error(host(v["dwu"]), dwur) < EXPECTED_BF16
+
+
+def test_empty_batch():
+    from fused_swiglu import FusedSwiGLU
+
+    x = torch.zeros(2, 0, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    wg = torch.ones(64, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    wu = torch.ones(64, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out = FusedSwiGLU.apply(x, wg, wu)
+    assert out.shape == (2, 0, 128)
+    out.sum().backward()
+    assert x.grad.shape == x.shape and torch.all(wg.grad == 0) and torch.all(wu.grad == 0)
+
+
+def test_inference_mode_skips_saved_activations():
+    from fusedswiglu_b200 import _launch
+
+    inp = orc.make_inputs(1, 192, 128, 256, "bf16", seed=9)
+    x, wg, wu = dev(inp["x"][0], "bf16"), dev(inp["w_gate"], "bf16"), dev(inp["w_up"], "bf16")
+    out1, g, u = _launch.forward(x, wg, wu, save_activations=True)
+    out2, g2, u2 = _launch.forward(x, wg, wu, save_activations=False)
+    assert g2 is None and u2 is None and torch.equal(out1, out2)
+
+
+def test_extreme_gate_values_stay_finite():
+    from fusedswiglu_b200 import _launch
+
+    x = torch.zeros(64, 64, device="cuda", dtype=torch.bfloat16)
+    x[:, 0] = torch.linspace(-300, 300, 64, device="cuda").bfloat16()
+    wg = torch.zeros(64, 64, device="cuda", dtype=torch.bfloat16)
+    wg[0, :] = 1.0
+    wu = wg.clone()
+    out, g, u = _launch.forward(x, wg, wu)
+    dg, du = _launch.gate_grad(torch.ones_like(out), g, u)
+    for t in (out, dg, du):
+        assert torch.all(torch.isfinite(t.float()))
+    ref = torch.nn.functional.silu(g.float()) * u.float()
+    assert rel_error(out, ref) < EXPECTED_BF16
+    assert torch.all(out[0].float() == 0)  # silu(-300) * (-300) -> -0 * -300 = 0
+
+
+# ------------------------------------- full-size, size-independent properties --
+def _full_size_inputs(T, dm, di, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(T, dm, device="cuda", dtype=torch.bfloat16, generator=g)
+    wg = torch.randn(dm, di, device="cuda", dtype=torch.bfloat16, generator=g) / math.sqrt(dm)
+    wu = torch.randn(dm, di, device="cuda", dtype=torch.bfloat16, generator=g) / math.sqrt(dm)
+    dout = torch.randn(T, di, device="cuda", dtype=torch.bfloat16, generator=g)
+    return x, wg, wu, dout
+
+
+@pytest.mark.parametrize("T,dm,di", [(8192, 4096, 12288), (32768, 4096, 14336)])
+def test_full_size_properties(T, dm, di):
+    """At the benchmark sizes: sampled rows/columns against fp64 dot products,
+    exact linearity of the backward in dout (scaling by 2 is exact in floating
+    point), and exact row-permutation equivariance of the forward."""
+    from fusedswiglu_b200 import _launch
+
+    x, wg, wu, dout = _full_size_inputs(T, dm, di)
+    out, g, u = _launch.forward(x, wg, wu)
+    rows = torch.randint(0, T, (64,), device="cuda")
+    g_ref = x[rows].double() @ wg.double()
+    u_ref = x[rows].double() @ wu.double()
+    o_ref = torch.nn.functional.silu(g_ref) * u_ref
+    assert rel_error(g[rows], g_ref) < EXPECTED_BF16
+    assert rel_error(u[rows], u_ref) < EXPECTED_BF16
+    assert rel_error(out[rows], o_ref) < EXPECTED_BF16
+
+    dg, du = _launch.gate_grad(dout, g, u)
+    dx = _launch.grad_input(dg, du, wg, wu)
+    dwg, dwu = _launch.grad_weights(x, dg, du)
+    dx_ref = dg[rows].double() @ wg.double().T + du[rows].double() @ wu.double().T
+    assert rel_error(dx[rows], dx_ref) < EXPECTED_BF16
+    cols = torch.randint(0, di, (32,), device="cuda")
+    dwg_ref = x.double().T @ dg[:, cols].double()
+    dwu_ref = x.double().T @ du[:, cols].double()
+    assert rel_error(dwg[:, cols], dwg_ref) < EXPECTED_BF16
+    assert rel_error(dwu[:, cols], dwu_ref) < EXPECTED_BF16
+
+    # linearity: backward(2*dout) == 2*backward(dout), bit for bit
+    dg2, du2 = _launch.gate_grad(dout * 2, g, u)
+    assert torch.equal(dg2, dg * 2) and torch.equal(du2, du * 2)
+    dx2 = _launch.grad_input(dg2, du2, wg, wu)
+    assert torch.equal(dx2, dx * 2)
+    dwg2, dwu2 = _launch.grad_weights(x, dg2, du2)
+    assert torch.equal(dwg2, dwg * 2) and torch.equal(dwu2, dwu * 2)
+    del dg2, du2, dx2, dwg2, dwu2
+
+    # permutation equivariance: reversing the tokens reverses the output rows
+    outp, _, _ = _launch.forward(x.flip(0).contiguous(), wg, wu, save_activations=False)
+    assert torch.equal(outp.flip(0), out)
