@@ -33,7 +33,9 @@ def swiglu_forward(ctx, x, w_gate, w_up, *, fast_accum: bool):
     x2d = x.contiguous().view(bs * sq, dm)
     wg = w_gate.contiguous()
     wu = w_up.contiguous()
-    need_grad = torch.is_grad_enabled() and (x.requires_grad or w_gate.requires_grad or w_up.requires_grad)
+    # Grad mode is always off inside Function.forward; what autograd will ask for
+    # is in ctx.needs_input_grad (all False under torch.no_grad()).
+    need_grad = any(ctx.needs_input_grad[:3])
     out, g, u = _launch.forward(x2d, wg, wu, fast_accum=fast_accum, save_activations=need_grad)
     if need_grad:
         ctx.save_for_backward(x2d, wg, wu, g, u)

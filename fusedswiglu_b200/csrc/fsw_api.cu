@@ -37,7 +37,8 @@ static int fail(int code, const char* fmt, ...) {
 // ----------------------------------------------------------------- options --
 struct Options {
   int64_t cta_group = 2;
-  int64_t group_m = 16;
+  int64_t nsub = 2;  // accumulator regions per tile (2 needs cta_group 2)
+  int64_t group_m = 8;
   // Debug overrides of the UMMA shared-memory descriptor fields (0 = built-in).
   int64_t k_lbo = 0, k_sbo = 0, k_kadv = 0;
   int64_t mn_lbo = 0, mn_sbo = 0, mn_kadv = 0;
@@ -46,6 +47,8 @@ static Options g_opt;
 
 // Status word the kernels write when a bounded wait gives up.
 __device__ uint32_t g_status_word;
+// SM cycles and nanoseconds that CTA 0 of the last GEMM launch was resident.
+__device__ unsigned long long g_clk_probe[2];
 
 // ------------------------------------------------------------ device cache --
 constexpr int kMaxDevices = 64;
@@ -55,6 +58,7 @@ struct DeviceInfo {
   int64_t smem_optin = 0;
   int max_pairs = 0;  // co-resident 2-CTA clusters of the GEMM kernels
   uint32_t* status = nullptr;
+  unsigned long long* clk_probe = nullptr;
 };
 static DeviceInfo g_dev[kMaxDevices];
 static std::mutex g_mu;
@@ -65,19 +69,19 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static EncodeTiledFn g_encode = nullptr;
 
-template <int MODE, int CG, typename T, bool ACC16>
+template <int MODE, int CG, int NSUB, typename T, bool ACC16>
 static cudaError_t prepare_kernel() {
-  return cudaFuncSetAttribute(gemm_kernel<MODE, CG, T, ACC16>,
+  return cudaFuncSetAttribute(gemm_kernel<MODE, CG, NSUB, T, ACC16>,
                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              TileCfg<MODE, CG>::SMEM_BYTES);
+                              TileCfg<MODE, CG, NSUB>::SMEM_BYTES);
 }
 
-template <int MODE, int CG>
+template <int MODE, int CG, int NSUB>
 static cudaError_t prepare_mode() {
   cudaError_t e;
-  if ((e = prepare_kernel<MODE, CG, __nv_bfloat16, false>()) != cudaSuccess) return e;
-  if ((e = prepare_kernel<MODE, CG, __half, false>()) != cudaSuccess) return e;
-  return prepare_kernel<MODE, CG, __half, true>();
+  if ((e = prepare_kernel<MODE, CG, NSUB, __nv_bfloat16, false>()) != cudaSuccess) return e;
+  if ((e = prepare_kernel<MODE, CG, NSUB, __half, false>()) != cudaSuccess) return e;
+  return prepare_kernel<MODE, CG, NSUB, __half, true>();
 }
 
 static int ensure_device(DeviceInfo** out) {
@@ -105,22 +109,27 @@ static int ensure_device(DeviceInfo** out) {
         return fail(FSW_EUNAVAILABLE, "driver does not provide cuTensorMapEncodeTiled");
       g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
-    FSW_CUDA((prepare_mode<MODE_FWD, 1>()));
-    FSW_CUDA((prepare_mode<MODE_DX, 1>()));
-    FSW_CUDA((prepare_mode<MODE_DW, 1>()));
-    FSW_CUDA((prepare_mode<MODE_FWD, 2>()));
-    FSW_CUDA((prepare_mode<MODE_DX, 2>()));
-    FSW_CUDA((prepare_mode<MODE_DW, 2>()));
+    FSW_CUDA((prepare_mode<MODE_FWD, 1, 1>()));
+    FSW_CUDA((prepare_mode<MODE_DX, 1, 1>()));
+    FSW_CUDA((prepare_mode<MODE_DW, 1, 1>()));
+    FSW_CUDA((prepare_mode<MODE_FWD, 2, 1>()));
+    FSW_CUDA((prepare_mode<MODE_DX, 2, 1>()));
+    FSW_CUDA((prepare_mode<MODE_DW, 2, 1>()));
+    FSW_CUDA((prepare_mode<MODE_FWD, 2, 2>()));
+    FSW_CUDA((prepare_mode<MODE_DX, 2, 2>()));
+    FSW_CUDA((prepare_mode<MODE_DW, 2, 2>()));
     void* sp = nullptr;
     FSW_CUDA(cudaGetSymbolAddress(&sp, g_status_word));
     d.status = static_cast<uint32_t*>(sp);
+    FSW_CUDA(cudaGetSymbolAddress(&sp, g_clk_probe));
+    d.clk_probe = static_cast<unsigned long long*>(sp);
     // How many CTA pairs can be resident at once (a GPC with an odd SM count
     // leaves one SM without a partner).
     {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2 * d.sm_count, 1, 1);
-      cfg.blockDim = dim3(TileCfg<MODE_FWD, 2>::THREADS, 1, 1);
-      cfg.dynamicSmemBytes = TileCfg<MODE_FWD, 2>::SMEM_BYTES;
+      cfg.blockDim = dim3(TileCfg<MODE_FWD, 2, 2>::THREADS, 1, 1);
+      cfg.dynamicSmemBytes = TileCfg<MODE_FWD, 2, 2>::SMEM_BYTES;
       cudaLaunchAttribute attr[1];
       attr[0].id = cudaLaunchAttributeClusterDimension;
       attr[0].val.clusterDim.x = 2;
@@ -130,7 +139,7 @@ static int ensure_device(DeviceInfo** out) {
       cfg.numAttrs = 1;
       int n = 0;
       cudaError_t e = cudaOccupancyMaxActiveClusters(
-          &n, gemm_kernel<MODE_FWD, 2, __nv_bfloat16, false>, &cfg);
+          &n, gemm_kernel<MODE_FWD, 2, 2, __nv_bfloat16, false>, &cfg);
       if (e != cudaSuccess || n <= 0) {
         (void)cudaGetLastError();
         n = d.sm_count / 2;
@@ -209,12 +218,12 @@ static void fill_operand_desc(int major, uint64_t* desc, uint32_t* kadv) {
 }
 
 // ---------------------------------------------------------------- launches --
-template <int MODE, int CG, typename T, bool ACC16>
+template <int MODE, int CG, int NSUB, typename T, bool ACC16>
 static cudaError_t launch_one(const GemmParams& p, int grid, cudaStream_t st) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(TileCfg<MODE, CG>::THREADS, 1, 1);
-  cfg.dynamicSmemBytes = TileCfg<MODE, CG>::SMEM_BYTES;
+  cfg.blockDim = dim3(TileCfg<MODE, CG, NSUB>::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = TileCfg<MODE, CG, NSUB>::SMEM_BYTES;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -223,15 +232,15 @@ static cudaError_t launch_one(const GemmParams& p, int grid, cudaStream_t st) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gemm_kernel<MODE, CG, T, ACC16>, p);
+  return cudaLaunchKernelEx(&cfg, gemm_kernel<MODE, CG, NSUB, T, ACC16>, p);
 }
 
-template <int MODE, int CG>
+template <int MODE, int CG, int NSUB>
 static cudaError_t launch_cg(const GemmParams& p, int grid, int dtype, bool acc16,
                              cudaStream_t st) {
-  if (dtype == FSW_BF16) return launch_one<MODE, CG, __nv_bfloat16, false>(p, grid, st);
-  if (acc16) return launch_one<MODE, CG, __half, true>(p, grid, st);
-  return launch_one<MODE, CG, __half, false>(p, grid, st);
+  if (dtype == FSW_BF16) return launch_one<MODE, CG, NSUB, __nv_bfloat16, false>(p, grid, st);
+  if (acc16) return launch_one<MODE, CG, NSUB, __half, true>(p, grid, st);
+  return launch_one<MODE, CG, NSUB, __half, false>(p, grid, st);
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -257,12 +266,14 @@ template <int MODE>
 static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t st,
                     DeviceInfo* d) {
   const int cg = (int)g_opt.cta_group;
+  const int nsub = (cg == 2) ? (int)g_opt.nsub : 1;
   const int tile_m = 128 * cg;
-  const int tile_n = (MODE == MODE_DX) ? 256 : 128;
+  const int tile_n = ((MODE == MODE_DX) ? 256 : 128) * nsub;
   p.num_m_tiles = (rows + tile_m - 1) / tile_m;
   p.num_n_tiles = (p.N + tile_n - 1) / tile_n;
   p.group_m = (int)g_opt.group_m < 1 ? 1 : (int)g_opt.group_m;
   p.status = d->status;
+  p.clk_probe = d->clk_probe;
   const int a_major = (MODE == MODE_DW) ? MAJOR_MN : MAJOR_K;
   const int b_major = (MODE == MODE_DX) ? MAJOR_K : MAJOR_MN;
   fill_operand_desc(a_major, &p.a_desc, &p.a_kadv);
@@ -274,10 +285,11 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   cudaError_t e;
   if (cg == 2) {
     const int pairs = (int)(tiles < d->max_pairs ? tiles : d->max_pairs);
-    e = launch_cg<MODE, 2>(p, 2 * pairs, dtype, acc16, st);
+    e = (nsub == 2) ? launch_cg<MODE, 2, 2>(p, 2 * pairs, dtype, acc16, st)
+                    : launch_cg<MODE, 2, 1>(p, 2 * pairs, dtype, acc16, st);
   } else {
     const int ctas = (int)(tiles < d->sm_count ? tiles : d->sm_count);
-    e = launch_cg<MODE, 1>(p, ctas, dtype, acc16, st);
+    e = launch_cg<MODE, 1, 1>(p, ctas, dtype, acc16, st);
   }
   if (e != cudaSuccess) return fail(FSW_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
   return FSW_OK;
@@ -394,6 +406,9 @@ int fsw_set_option(const char* name, int64_t value) {
   if (!strcmp(name, "cta_group")) {
     if (value != 1 && value != 2) return fail(FSW_EINVAL, "cta_group must be 1 or 2");
     g_opt.cta_group = value;
+  } else if (!strcmp(name, "nsub")) {
+    if (value != 1 && value != 2) return fail(FSW_EINVAL, "nsub must be 1 or 2");
+    g_opt.nsub = value;
   } else if (!strcmp(name, "group_m")) {
     if (value < 1 || value > (1 << 20)) return fail(FSW_EINVAL, "group_m must be >= 1");
     g_opt.group_m = value;
@@ -419,19 +434,30 @@ int64_t fsw_get_option(const char* name) {
   if (name == nullptr) return -1;
   if (!strcmp(name, "cta_group")) return g_opt.cta_group;
   if (!strcmp(name, "group_m")) return g_opt.group_m;
+  if (!strcmp(name, "nsub")) return g_opt.nsub;
   if (!strcmp(name, "k_lbo")) return g_opt.k_lbo;
   if (!strcmp(name, "k_sbo")) return g_opt.k_sbo;
   if (!strcmp(name, "k_kadv")) return g_opt.k_kadv;
   if (!strcmp(name, "mn_lbo")) return g_opt.mn_lbo;
   if (!strcmp(name, "mn_sbo")) return g_opt.mn_sbo;
   if (!strcmp(name, "mn_kadv")) return g_opt.mn_kadv;
+  if (!strcmp(name, "last_sm_khz")) {
+    // Synchronises; average SM clock (kHz) seen by CTA 0 of the last GEMM launch.
+    DeviceInfo* d = nullptr;
+    if (ensure_device(&d) != FSW_OK) return -1;
+    unsigned long long v[2] = {0, 0};
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpy(v, d->clk_probe, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return v[1] ? (int64_t)(v[0] * 1000000ull / v[1]) : -1;
+  }
   if (!strcmp(name, "max_pairs") || !strcmp(name, "sm_count") || !strcmp(name, "stages")) {
     // facts about the current device (initialises it on first use)
     DeviceInfo* d = nullptr;
     if (ensure_device(&d) != FSW_OK) return -1;
     if (!strcmp(name, "max_pairs")) return d->max_pairs;
     if (!strcmp(name, "sm_count")) return d->sm_count;
-    return g_opt.cta_group == 2 ? TileCfg<MODE_FWD, 2>::STAGES : TileCfg<MODE_FWD, 1>::STAGES;
+    if (g_opt.cta_group == 1) return TileCfg<MODE_FWD, 1, 1>::STAGES;
+    return g_opt.nsub == 2 ? TileCfg<MODE_FWD, 2, 2>::STAGES : TileCfg<MODE_FWD, 2, 1>::STAGES;
   }
   return -1;
 }
@@ -455,9 +481,6 @@ int fsw_forward(const void* x, const void* w_gate, const void* w_up, void* out, 
   p.a1 = p.a0;
   if ((rc = make_map(&p.b0, w_gate, dtype, di, dm, 64, "w_gate")) != FSW_OK) return rc;
   if ((rc = make_map(&p.b1, w_up, dtype, di, dm, 64, "w_up")) != FSW_OK) return rc;
-  if ((rc = make_map(&p.c0, g ? g : out, dtype, di, T, 32, "g")) != FSW_OK) return rc;
-  if ((rc = make_map(&p.c1, u ? u : out, dtype, di, T, 32, "u")) != FSW_OK) return rc;
-  if ((rc = make_map(&p.c2, out, dtype, di, T, 32, "out")) != FSW_OK) return rc;
   p.M = (int)T;
   p.N = (int)di;
   p.num_k_blocks = (int)((dm + 63) / 64);
@@ -516,9 +539,6 @@ int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const vo
   if ((rc = make_map(&p.a1, du, dtype, di, T, 128, "du")) != FSW_OK) return rc;
   if ((rc = make_map(&p.b0, w_gate, dtype, di, dm, 256 / cg, "w_gate")) != FSW_OK) return rc;
   if ((rc = make_map(&p.b1, w_up, dtype, di, dm, 256 / cg, "w_up")) != FSW_OK) return rc;
-  if ((rc = make_map(&p.c0, dx, dtype, dm, T, 32, "dx")) != FSW_OK) return rc;
-  p.c1 = p.c0;
-  p.c2 = p.c0;
   p.c0_ptr = dx;
   p.M = (int)T;
   p.N = (int)dm;
@@ -550,9 +570,6 @@ int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate
   p.a1 = p.a0;
   if ((rc = make_map(&p.b0, dg, dtype, di, T, 64, "dg")) != FSW_OK) return rc;
   if ((rc = make_map(&p.b1, du, dtype, di, T, 64, "du")) != FSW_OK) return rc;
-  if ((rc = make_map(&p.c0, dw_gate, dtype, di, dm, 32, "dw_gate")) != FSW_OK) return rc;
-  if ((rc = make_map(&p.c1, dw_up, dtype, di, dm, 32, "dw_up")) != FSW_OK) return rc;
-  p.c2 = p.c0;
   p.c0_ptr = dw_gate;
   p.c1_ptr = dw_up;
   p.M = (int)dm;

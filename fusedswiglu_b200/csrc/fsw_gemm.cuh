@@ -7,17 +7,25 @@
 //              one accumulator, the K loop runs over both products
 //   MODE_DW  : [dW_gate | dW_up] = x^T @ [dg | du]   (A MN-major, B MN-major)
 //
-// One CTA owns 128 accumulator rows x 256 fp32 columns of tensor memory, twice
-// (two accumulator stages), so the epilogue of tile i overlaps the MMAs of tile
-// i+1.  With CG == 2 two CTAs of a cluster form a pair: each stages its own 128
-// rows of A and half (128) of the 256 B columns, the pair leader issues
-// M=256 x N=256 MMAs that read both CTAs' shared memory and write both CTAs'
-// tensor memory.  No TMA multicast is used anywhere.
+// One CTA owns 128 rows x 512 fp32 columns of tensor memory, used as two
+// 256-column accumulator regions.
+//   NSUB == 1: a tile is 128 x 256 per CTA; the two regions alternate between
+//              consecutive tiles, so the epilogue of tile i overlaps the MMAs of
+//              tile i+1.
+//   NSUB == 2: a tile is 128 x 512 per CTA and fills both regions; per K block
+//              the A tile is staged once and used by two N=256 MMAs, which cuts
+//              L2->shared-memory traffic per flop by a quarter.  The epilogue is
+//              not overlapped with MMAs, only with the operand prefetch.
+// With CG == 2 two CTAs of a cluster form a pair: each stages its own 128 rows
+// of A and half of every B sub-tile; the pair leader issues M=256 x N=256 MMAs
+// that read both CTAs' shared memory and write both CTAs' tensor memory.  No TMA
+// multicast is used anywhere.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner and MMA
-// issuer, warps 2..5 = epilogue (TMEM -> registers -> swizzled smem -> TMA store).
+// Warp roles: warp 0 = TMA producer (one thread), warp 1 = TMEM owner and MMA
+// issuer (one thread), warps 2.. = epilogue (TMEM -> registers -> 16-bit results
+// -> per-warp shared-memory transpose -> row-coalesced 16-byte global stores).
 //
-// Every mbarrier wait is bounded: after kWaitLimitNs the waiting warp records a
+// Every mbarrier wait is bounded: after kWaitLimitNs the waiting thread records a
 // code in `status`, raises the CTA's abort flag and every role leaves its loop;
 // the CTA then lets in-flight copies drain, frees its tensor memory and returns.
 #pragma once
@@ -44,7 +52,6 @@ constexpr uint64_t kDrainNs = 20000000ull;        // 20 ms drain on the abort pa
 struct GemmParams {
   CUtensorMap a0, a1;      // A operand(s); a1 only in MODE_DX (second product)
   CUtensorMap b0, b1;      // B operands (gate, up)
-  CUtensorMap c0, c1, c2;  // outputs (see the mode table above)
   uint64_t a_desc, b_desc; // UMMA shared-memory descriptors with a zero start address
   uint32_t a_kadv, b_kadv; // bytes to advance the start address per K=16 step
   uint32_t idesc;          // UMMA instruction descriptor
@@ -53,44 +60,61 @@ struct GemmParams {
   int num_k_blocks;        // 64-wide K blocks per product
   int store_gu;            // MODE_FWD: also write g and u
   uint32_t* status;        // device status word (0 = ok)
-  void *c0_ptr, *c1_ptr, *c2_ptr;  // raw output pointers (direct-store epilogue)
+  void *c0_ptr, *c1_ptr, *c2_ptr;  // outputs (see the mode table above); row stride N
+  unsigned long long* clk_probe;   // [2]: SM cycles and nanoseconds CTA 0 was resident
 };
 
-// Epilogue store path: 0 = stage 32x64 boxes in swizzled shared memory and let TMA
-// write them; 1 = 16-byte global stores straight from registers, which frees the
-// staging space for more operand stages.
-#ifndef FSW_EPI_DIRECT
-#define FSW_EPI_DIRECT 0
+// Epilogue warps: 4 (one per TMEM lane quadrant) or 8 (two per quadrant).
+#ifndef FSW_EPI_WARPS
+#define FSW_EPI_WARPS 8
 #endif
 constexpr int kSmemBudget = 232448;  // 227 KB opt-in limit per CTA
 
-template <int MODE, int CG>
+// Timing experiments only (results are garbage when set): run the MMA loop on
+// whatever is in shared memory without any TMA load, or skip the epilogue's
+// math and stores.  All default to off and are never set in the shipped build.
+#ifndef FSW_DBG_SKIP_LOADS
+#define FSW_DBG_SKIP_LOADS 0
+#endif
+#ifndef FSW_DBG_SKIP_EPILOGUE
+#define FSW_DBG_SKIP_EPILOGUE 0
+#endif
+#ifndef FSW_DBG_SKIP_B_LOADS
+#define FSW_DBG_SKIP_B_LOADS 0
+#endif
+
+template <int MODE, int CG, int NSUB>
 struct TileCfg {
+  static_assert(NSUB == 1 || (NSUB == 2 && CG == 2), "512-column tiles need a CTA pair");
   static constexpr int A_MAJOR = (MODE == MODE_DW) ? MAJOR_MN : MAJOR_K;
   static constexpr int B_MAJOR = (MODE == MODE_DX) ? MAJOR_K : MAJOR_MN;
   static constexpr int BM = 128;          // accumulator rows per CTA
-  static constexpr int BN = 256;          // accumulator columns per CTA (MMA N)
+  static constexpr int BN = 256;          // columns of one accumulator region (MMA N)
   static constexpr int BK = 64;           // one 128-byte swizzle row of 16-bit elements
-  static constexpr int B_ROWS = BN / CG;  // B n-extent staged by each CTA
+  static constexpr int SUB_ROWS = BN / CG;            // B n-extent per region staged by a CTA
+  static constexpr int SUB_B_BYTES = SUB_ROWS * BK * 2;
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = B_ROWS * BK * 2;
+  static constexpr int B_BYTES = NSUB * SUB_B_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int CHUNK_BYTES = 64 * BK * 2;  // one MN-major 64x64 box
-  static constexpr bool EPI_DIRECT = FSW_EPI_DIRECT != 0;
-  static constexpr int EPI_WARPS = 4;
-  static constexpr int EPI_NBUF = 3;
-  static constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows x 64 16-bit columns
-  static constexpr int EPI_BYTES = EPI_DIRECT ? 0 : EPI_WARPS * EPI_NBUF * EPI_BUF_BYTES;
+  static constexpr int EPI_WARPS = FSW_EPI_WARPS;
+  static_assert(EPI_WARPS == 4 || EPI_WARPS == 8, "4 or 8 epilogue warps");
+  static constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows x 64 16-bit columns per warp
+  static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUF_BYTES;
   static constexpr int BAR_BYTES = 256;
   // as many operand stages as fit beside the epilogue staging
   static constexpr int STAGES = (kSmemBudget - 1024 - BAR_BYTES - EPI_BYTES) / STAGE_BYTES;
+  static_assert(STAGES >= 2 && STAGES <= 12, "unexpected stage count");
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;
-  static constexpr int THREADS = 192;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int TMEM_COLS = 512;
   static constexpr int NSEG = (MODE == MODE_DX) ? 2 : 1;
-  // Output columns covered by one tile, per output tensor.
-  static constexpr int TILE_N = (MODE == MODE_DX) ? 256 : 128;
+  // Output columns covered by one accumulator region / one tile, per output tensor.
+  static constexpr int REGION_N = (MODE == MODE_DX) ? 256 : 128;
+  static constexpr int TILE_N = REGION_N * NSUB;
   static constexpr int TILE_M = BM * CG;
+  // Arrivals that free one accumulator region.
+  static constexpr int TEMPTY_COUNT = (NSUB == 2 ? 4 : EPI_WARPS) * CG;
 };
 
 // ------------------------------------------------------------- conversions --
@@ -117,7 +141,15 @@ __device__ __forceinline__ float round16<__half>(float v) {
   return __half2float(__float2half_rn(v));
 }
 
-__device__ __forceinline__ float sigmoid_f32(float x) { return __frcp_rn(1.0f + __expf(-x)); }
+// 1 / (1 + 2^(-x*log2(e))) with the two special-function-unit approximations
+// (relative error ~1e-7, far below a 16-bit ulp).  x -> -inf gives exactly 0,
+// x -> +inf exactly 1.
+__device__ __forceinline__ float sigmoid_f32(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return r;
+}
 
 // ------------------------------------------------------------ bounded wait --
 struct AbortCtl {
@@ -125,28 +157,29 @@ struct AbortCtl {
   uint32_t* status;         // global status word
 };
 
-__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const AbortCtl& ctl,
-                                             uint32_t code) {
-  bool ok = ptx::mbar_try_wait(bar, parity);
-  if (!ok) {
-    const uint64_t t0 = ptx::globaltimer_ns();
-    uint32_t spins = 0;
-    for (;;) {
-      if (ptx::mbar_try_wait(bar, parity)) {
-        ok = true;
-        break;
-      }
-      if ((++spins & 255u) == 0u) {
-        if (*ctl.flag != 0u) break;
-        if (ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
-          *ctl.flag = code;
-          atomicCAS(ctl.status, 0u, code | (static_cast<uint32_t>(blockIdx.x) << 8));
-          break;
-        }
+// Wait by ONE thread.
+__device__ __forceinline__ bool bounded_wait_thread(uint32_t bar, uint32_t parity,
+                                                    const AbortCtl& ctl, uint32_t code) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 255u) == 0u) {
+      if (*ctl.flag != 0u) return false;
+      if (ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
+        *ctl.flag = code;
+        atomicCAS(ctl.status, 0u, code | (static_cast<uint32_t>(blockIdx.x) << 8));
+        return false;
       }
     }
   }
-  return __all_sync(0xffffffffu, ok);
+}
+
+// Wait by a whole (converged) warp; the verdict is made warp-uniform.
+__device__ __forceinline__ bool bounded_wait_warp(uint32_t bar, uint32_t parity,
+                                                  const AbortCtl& ctl, uint32_t code) {
+  return __all_sync(0xffffffffu, bounded_wait_thread(bar, parity, ctl, code));
 }
 
 // Linear tile index -> (m_tile, n_tile); m is grouped so that concurrently
@@ -161,10 +194,163 @@ __device__ __forceinline__ void decode_tile(int t, const GemmParams& p, int& m_t
   n_tile = r / gsz;
 }
 
+// ---------------------------------------------------------------- epilogue --
+// tcgen05.ld hands every thread 32 consecutive columns of ONE accumulator row, so
+// a direct store would scatter each warp-wide store over 32 rows.  The epilogue
+// instead transposes through a 4 KB per-warp shared-memory buffer: threads write
+// their row (XOR-swizzled 16-byte chunks, conflict-free), then read it back so that
+// 4 (or 8) consecutive lanes cover one row and every global store instruction
+// writes whole 64- or 128-byte row segments.
+struct EpiCtx {
+  int lane;
+  int row0;       // first global output row of this warp
+  uint32_t buf;   // this warp's 4 KB staging buffer
+};
+
+// 32 rows x 32 columns (64-byte rows) held as 16 packed words per thread.
+__device__ __forceinline__ void stage_rows64(uint32_t buf, int lane, const uint32_t (&w)[16]) {
+  const uint32_t base = buf + lane * 64u;
+  const uint32_t x = (lane >> 1) & 3u;
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    ptx::st_shared_v4(base + ((c ^ x) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+}
+// Write the staged 32x32 block to out[row0.., col0..] (row stride N elements).
+__device__ __forceinline__ void flush_rows64(uint32_t buf, int lane, void* out, int row0, int col0,
+                                             int M, int N) {
+  const int c = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = 8 * i + (lane >> 2);
+    uint32_t a, b, cc, d;
+    ptx::ld_shared_v4(buf + r * 64u + ((c ^ ((r >> 1) & 3)) << 4), a, b, cc, d);
+    const int row = row0 + r, col = col0 + c * 8;
+    if (row < M && col < N)
+      ptx::st_global_v4(static_cast<char*>(out) + (static_cast<size_t>(row) * N + col) * 2, a, b, cc,
+                        d);
+  }
+}
+// 32 rows x 64 columns (128-byte rows) held as 32 packed words per thread.
+__device__ __forceinline__ void stage_rows128(uint32_t buf, int lane, const uint32_t (&w)[32]) {
+  const uint32_t base = buf + lane * 128u;
+  const uint32_t x = lane & 7u;
+#pragma unroll
+  for (int c = 0; c < 8; ++c)
+    ptx::st_shared_v4(base + ((c ^ x) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+}
+__device__ __forceinline__ void flush_rows128(uint32_t buf, int lane, void* out, int row0, int col0,
+                                              int M, int N) {
+  const int c = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = 4 * i + (lane >> 3);
+    uint32_t a, b, cc, d;
+    ptx::ld_shared_v4(buf + r * 128u + ((c ^ (r & 7)) << 4), a, b, cc, d);
+    const int row = row0 + r, col = col0 + c * 8;
+    if (row < M && col < N)
+      ptx::st_global_v4(static_cast<char*>(out) + (static_cast<size_t>(row) * N + col) * 2, a, b, cc,
+                        d);
+  }
+}
+
+// SwiGLU epilogue over one 256-column region laid out [128 gate | 128 up]:
+// 64-column boxes jb in [jb_begin, jb_end).  `release` is called right after
+// the last tensor-memory read.
+template <class C, typename T, bool ACC16, class Release>
+__device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& e, uint32_t taddr,
+                                             int n0, int jb_begin, int jb_end, Release release) {
+  const uint32_t buf0 = e.buf, buf1 = e.buf + 2048u;
+#pragma unroll 1
+  for (int jb = jb_begin; jb < jb_end; ++jb) {
+#pragma unroll 1
+    for (int h = 0; h < 2; ++h) {
+      uint32_t rg[32], ru[32];
+      ptx::tmem_ld_32x32(taddr + jb * 64 + h * 32, rg);
+      ptx::tmem_ld_32x32(taddr + 128 + jb * 64 + h * 32, ru);
+      ptx::tmem_ld_wait();
+      if (jb == jb_end - 1 && h == 1) release();
+      uint32_t pg[16], pu[16], po[16];
+#pragma unroll
+      for (int q = 0; q < 16; ++q) {
+        const int c0 = 2 * q;
+        if (ACC16) {
+          // fp16 accumulators sit in the low half of each 32-bit column.
+          const __half g0 = __ushort_as_half(static_cast<unsigned short>(rg[c0]));
+          const __half g1 = __ushort_as_half(static_cast<unsigned short>(rg[c0 + 1]));
+          const __half u0 = __ushort_as_half(static_cast<unsigned short>(ru[c0]));
+          const __half u1 = __ushort_as_half(static_cast<unsigned short>(ru[c0 + 1]));
+          const float gf0 = __half2float(g0), gf1 = __half2float(g1);
+          const __half s0 = __float2half_rn(gf0 * sigmoid_f32(gf0));
+          const __half s1 = __float2half_rn(gf1 * sigmoid_f32(gf1));
+          const __half2 o = __hmul2(__halves2half2(u0, u1), __halves2half2(s0, s1));
+          pg[q] = (rg[c0] & 0xFFFFu) | (rg[c0 + 1] << 16);
+          pu[q] = (ru[c0] & 0xFFFFu) | (ru[c0 + 1] << 16);
+          po[q] = *reinterpret_cast<const uint32_t*>(&o);
+        } else {
+          const float g0 = __uint_as_float(rg[c0]), g1 = __uint_as_float(rg[c0 + 1]);
+          const float u0 = __uint_as_float(ru[c0]), u1 = __uint_as_float(ru[c0 + 1]);
+          const float s0 = round16<T>(g0 * sigmoid_f32(g0));
+          const float s1 = round16<T>(g1 * sigmoid_f32(g1));
+          pg[q] = pack2<T>(g0, g1);
+          pu[q] = pack2<T>(u0, u1);
+          po[q] = pack2<T>(u0 * s0, u1 * s1);
+        }
+      }
+      const int col = n0 + jb * 64 + h * 32;
+      if (p.store_gu) {
+        stage_rows64(buf0, e.lane, pg);
+        stage_rows64(buf1, e.lane, pu);
+        __syncwarp();
+        flush_rows64(buf0, e.lane, p.c0_ptr, e.row0, col, p.M, p.N);
+        flush_rows64(buf1, e.lane, p.c1_ptr, e.row0, col, p.M, p.N);
+        __syncwarp();
+      }
+      stage_rows64(buf0, e.lane, po);
+      __syncwarp();
+      flush_rows64(buf0, e.lane, p.c2_ptr, e.row0, col, p.M, p.N);
+      __syncwarp();
+    }
+  }
+}
+
+// Plain epilogue over one 256-column region: 64-column boxes jb in
+// [jb_begin, jb_end).  MODE_DX: all four boxes belong to c0 at columns
+// n0 + 64*jb; MODE_DW: boxes 0,1 -> c0, boxes 2,3 -> c1, at n0 + 64*(jb&1).
+template <class C, int MODE, typename T, bool ACC16, class Release>
+__device__ __forceinline__ void drain_plain(const GemmParams& p, const EpiCtx& e, uint32_t taddr,
+                                            int n0, int jb_begin, int jb_end, Release release) {
+#pragma unroll 1
+  for (int jb = jb_begin; jb < jb_end; ++jb) {
+    uint32_t r0[32], r1[32];
+    ptx::tmem_ld_32x32(taddr + jb * 64, r0);
+    ptx::tmem_ld_32x32(taddr + jb * 64 + 32, r1);
+    ptx::tmem_ld_wait();
+    if (jb == jb_end - 1) release();
+    uint32_t pk[32];
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {
+      if (ACC16) {
+        pk[q] = (r0[2 * q] & 0xFFFFu) | (r0[2 * q + 1] << 16);
+        pk[16 + q] = (r1[2 * q] & 0xFFFFu) | (r1[2 * q + 1] << 16);
+      } else {
+        pk[q] = pack2<T>(__uint_as_float(r0[2 * q]), __uint_as_float(r0[2 * q + 1]));
+        pk[16 + q] = pack2<T>(__uint_as_float(r1[2 * q]), __uint_as_float(r1[2 * q + 1]));
+      }
+    }
+    const int col = (MODE == MODE_DX) ? (n0 + jb * 64) : (n0 + (jb & 1) * 64);
+    void* out = (MODE == MODE_DW && jb >= 2) ? p.c1_ptr : p.c0_ptr;
+    stage_rows128(e.buf, e.lane, pk);
+    __syncwarp();
+    flush_rows128(e.buf, e.lane, out, e.row0, col, p.M, p.N);
+    __syncwarp();
+  }
+}
+
 // ------------------------------------------------------------------ kernel --
-template <int MODE, int CG, typename T, bool ACC16>
-__global__ void __launch_bounds__(192, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
-  using C = TileCfg<MODE, CG>;
+template <int MODE, int CG, int NSUB, typename T, bool ACC16>
+__global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
+    gemm_kernel(const __grid_constant__ GemmParams p) {
+  using C = TileCfg<MODE, CG, NSUB>;
   constexpr int STAGES = C::STAGES;
 
   extern __shared__ uint8_t smem_raw[];
@@ -186,6 +372,13 @@ __global__ void __launch_bounds__(192, 1) gemm_kernel(const __grid_constant__ Ge
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t cta_rank = (CG == 2) ? ptx::cluster_ctarank() : 0u;
+  // CTA 0 measures the SM clock it actually ran at (cycles / wall time).
+  long long probe_c0 = 0;
+  uint64_t probe_t0 = 0;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    probe_c0 = clock64();
+    probe_t0 = ptx::globaltimer_ns();
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -194,7 +387,7 @@ __global__ void __launch_bounds__(192, 1) gemm_kernel(const __grid_constant__ Ge
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
-      ptx::mbar_init(tempty_bar(a), C::EPI_WARPS * CG);
+      ptx::mbar_init(tempty_bar(a), C::TEMPTY_COUNT);
     }
     *abort_flag = 0u;
     ptx::fence_mbar_init();
@@ -203,10 +396,7 @@ __global__ void __launch_bounds__(192, 1) gemm_kernel(const __grid_constant__ Ge
     ptx::prefetch_tensormap(&p.a0);
     ptx::prefetch_tensormap(&p.b0);
     ptx::prefetch_tensormap(&p.b1);
-    ptx::prefetch_tensormap(&p.c0);
     if (MODE == MODE_DX) ptx::prefetch_tensormap(&p.a1);
-    if (MODE != MODE_DX) ptx::prefetch_tensormap(&p.c1);
-    if (MODE == MODE_FWD) ptx::prefetch_tensormap(&p.c2);
   }
   if (warp == 1) {
     ptx::tmem_alloc<CG>(bar_base + 8u * (2 * STAGES + 4), C::TMEM_COLS);
@@ -227,27 +417,28 @@ __global__ void __launch_bounds__(192, 1) gemm_kernel(const __grid_constant__ Ge
   const int num_kb = p.num_k_blocks;
 
   if (warp == 0) {
-    // ======================= TMA producer =======================
-    int s = 0;
-    uint32_t ph = 0;
-    bool ok = true;
-    const uint32_t rank_off = cta_rank * C::B_ROWS;
-    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-      int m_tile, n_tile;
-      decode_tile(t, p, m_tile, n_tile);
-      const int m0 = m_tile * C::TILE_M + cta_rank * C::BM;
-      const int n0 = n_tile * C::TILE_N;
-      for (int seg = 0; seg < C::NSEG && ok; ++seg) {
-        for (int kb = 0; kb < num_kb; ++kb) {
-          ok = bounded_wait(empty_bar(s), ph ^ 1u, ctl, WAIT_PRODUCER_EMPTY);
-          if (!ok) break;
-          if (lane == 0) {
+    // ======================= TMA producer (one thread) =======================
+    if (lane == 0 && !FSW_DBG_SKIP_LOADS) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        int m_tile, n_tile;
+        decode_tile(t, p, m_tile, n_tile);
+        const int m0 = m_tile * C::TILE_M + cta_rank * C::BM;
+        const int n0 = n_tile * C::TILE_N;
+        for (int seg = 0; seg < C::NSEG && ok; ++seg) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            ok = bounded_wait_thread(empty_bar(s), ph ^ 1u, ctl, WAIT_PRODUCER_EMPTY);
+            if (!ok) break;
             const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
             const uint32_t b_dst = a_dst + C::A_BYTES;
             const int k0 = kb * C::BK;
             uint32_t fb = full_bar(s);
             if (CG == 2) fb = ptx::mapa(fb, 0);
-            if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(s), CG * C::STAGE_BYTES);
+            if (cta_rank == 0)
+              ptx::mbar_arrive_expect_tx(full_bar(s),
+                                         CG * (FSW_DBG_SKIP_B_LOADS ? C::A_BYTES : C::STAGE_BYTES));
             auto load = [&](uint32_t dst, const CUtensorMap* tm, int x, int y) {
               if (CG == 2)
                 ptx::tma_load_2d_pair(dst, tm, fb, x, y);
@@ -262,243 +453,158 @@ __global__ void __launch_bounds__(192, 1) gemm_kernel(const __grid_constant__ Ge
               for (int c = 0; c < C::BM / 64; ++c)
                 load(a_dst + c * C::CHUNK_BYTES, &p.a0, m0 + c * 64, k0);
             }
-            // ---- B tile: B_ROWS n x 64 k
-            if (C::B_MAJOR == MAJOR_K) {
-              load(b_dst, seg == 1 ? &p.b1 : &p.b0, k0, n0 + rank_off);
-            } else if (CG == 1) {
+            // ---- B: one SUB_ROWS x 64 sub-tile per accumulator region
+            if (!FSW_DBG_SKIP_B_LOADS) {
 #pragma unroll
-              for (int c = 0; c < 4; ++c)
-                load(b_dst + c * C::CHUNK_BYTES, c < 2 ? &p.b0 : &p.b1, n0 + (c & 1) * 64, k0);
-            } else {
+              for (int r = 0; r < NSUB; ++r) {
+                const uint32_t dst = b_dst + r * C::SUB_B_BYTES;
+                if (C::B_MAJOR == MAJOR_K) {
+                  load(dst, seg == 1 ? &p.b1 : &p.b0, k0,
+                       n0 + r * C::REGION_N + cta_rank * C::SUB_ROWS);
+                } else if (CG == 1) {
 #pragma unroll
-              for (int c = 0; c < 2; ++c)
-                load(b_dst + c * C::CHUNK_BYTES, cta_rank ? &p.b1 : &p.b0, n0 + c * 64, k0);
+                  for (int c = 0; c < 4; ++c)
+                    load(dst + c * C::CHUNK_BYTES, c < 2 ? &p.b0 : &p.b1, n0 + (c & 1) * 64, k0);
+                } else {
+#pragma unroll
+                  for (int c = 0; c < 2; ++c)
+                    load(dst + c * C::CHUNK_BYTES, cta_rank ? &p.b1 : &p.b0,
+                         n0 + r * C::REGION_N + c * 64, k0);
+                }
+              }
             }
-          }
-          __syncwarp();
-          if (++s == STAGES) {
-            s = 0;
-            ph ^= 1u;
+            if (++s == STAGES) {
+              s = 0;
+              ph ^= 1u;
+            }
           }
         }
       }
     }
   } else if (warp == 1) {
-    // ======================= MMA issuer (pair leader only) =======================
-    if (cta_rank == 0) {
+    // ================ MMA issuer (one thread of the pair leader) ================
+    if (cta_rank == 0 && lane == 0) {
       int s = 0, a = 0;
       uint32_t ph = 0, aph = 0;
       bool ok = true;
+      auto commit = [&](uint32_t bar) {
+        if (CG == 2)
+          ptx::mma_commit_pair(bar, 3);
+        else
+          ptx::mma_commit(bar);
+      };
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-        ok = bounded_wait(tempty_bar(a), aph ^ 1u, ctl, WAIT_MMA_TMEM_EMPTY);
-        if (!ok) break;
-        ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + a * C::BN;
-        uint32_t accumulate = 0;
-        for (int it = 0; it < C::NSEG * num_kb; ++it) {
-          ok = bounded_wait(full_bar(s), ph, ctl, WAIT_MMA_FULL);
+        if (NSUB == 1) {
+          ok = bounded_wait_thread(tempty_bar(a), aph ^ 1u, ctl, WAIT_MMA_TMEM_EMPTY);
           if (!ok) break;
           ptx::tc_fence_after_sync();
-          if (lane == 0) {
-            const uint32_t a_addr = smem_base + s * C::STAGE_BYTES;
-            const uint32_t b_addr = a_addr + C::A_BYTES;
+        }
+        const int iters = C::NSEG * num_kb;
+        for (int it = 0; it < iters; ++it) {
+          if (!FSW_DBG_SKIP_LOADS) ok = bounded_wait_thread(full_bar(s), ph, ctl, WAIT_MMA_FULL);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + s * C::STAGE_BYTES;
+          const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+          for (int r = 0; r < NSUB; ++r) {
+            if (NSUB == 2 && it == 0) {
+              // both regions belong to this tile; region r must have been drained
+              ok = bounded_wait_thread(tempty_bar(r), aph ^ 1u, ctl, WAIT_MMA_TMEM_EMPTY);
+              if (!ok) break;
+              ptx::tc_fence_after_sync();
+            }
+            const uint32_t d_tmem = tmem_base + (NSUB == 2 ? r : a) * C::BN;
 #pragma unroll
             for (int k = 0; k < C::BK / 16; ++k) {
               const uint64_t ad = p.a_desc | (((a_addr + k * p.a_kadv) & 0x3FFFFu) >> 4);
-              const uint64_t bd = p.b_desc | (((b_addr + k * p.b_kadv) & 0x3FFFFu) >> 4);
-              ptx::mma_f16_ss<CG>(d_tmem, ad, bd, p.idesc, accumulate);
-              accumulate = 1;
+              const uint64_t bd =
+                  p.b_desc | (((b_addr + r * C::SUB_B_BYTES + k * p.b_kadv) & 0x3FFFFu) >> 4);
+              ptx::mma_f16_ss<CG>(d_tmem, ad, bd, p.idesc, (it | k) != 0 ? 1u : 0u);
             }
-            if (CG == 2)
-              ptx::mma_commit_pair(empty_bar(s), 3);
-            else
-              ptx::mma_commit(empty_bar(s));
           }
-          __syncwarp();
-          accumulate = 1;
+          if (!ok) break;
+          commit(empty_bar(s));
           if (++s == STAGES) {
             s = 0;
             ph ^= 1u;
           }
         }
         if (!ok) break;
-        if (lane == 0) {
-          if (CG == 2)
-            ptx::mma_commit_pair(tfull_bar(a), 3);
-          else
-            ptx::mma_commit(tfull_bar(a));
+        if (NSUB == 2) {
+          commit(tfull_bar(0));
+          aph ^= 1u;
+        } else {
+          commit(tfull_bar(a));
+          a ^= 1;
+          if (a == 0) aph ^= 1u;
         }
-        __syncwarp();
-        a ^= 1;
-        if (a == 0) aph ^= 1u;
       }
     }
   } else {
     // ======================= epilogue =======================
     const int q = warp & 3;     // TMEM lane quadrant this warp may read
-    const int ew = warp - 2;    // staging-buffer owner index
-    const uint32_t my_epi = epi_base + ew * C::EPI_NBUF * C::EPI_BUF_BYTES;
-    const uint32_t row_off = lane * 128u;
-    const uint32_t sw = lane & 7u;
-    int a = 0, rb = 0;
+    const int ew = warp - 2;    // epilogue warp index
+    const int chalf = ew >> 2;  // with 8 warps: 0 or 1
+    constexpr int kSplit = C::EPI_WARPS / 4;
+    EpiCtx e;
+    e.lane = lane;
+    e.buf = epi_base + ew * C::EPI_BUF_BYTES;
+    int a = 0;
     uint32_t aph = 0;
     bool ok = true;
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
       int m_tile, n_tile;
       decode_tile(t, p, m_tile, n_tile);
-      const int row0 = m_tile * C::TILE_M + cta_rank * C::BM + q * 32;
+      e.row0 = m_tile * C::TILE_M + cta_rank * C::BM + q * 32;
       const int n0 = n_tile * C::TILE_N;
-      ok = bounded_wait(tfull_bar(a), aph, ctl, WAIT_EPI_TMEM_FULL);
+      ok = bounded_wait_warp(tfull_bar(NSUB == 2 ? 0 : a), aph, ctl, WAIT_EPI_TMEM_FULL);
       if (!ok) break;
       ptx::tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * C::BN;
+      const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 
-      auto release_tmem = [&]() {
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          if (CG == 2)
-            ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(a), 0));
-          else
-            ptx::mbar_arrive(tempty_bar(a));
-        }
-      };
-
-      if (MODE == MODE_FWD) {
-        const uint32_t buf_g = my_epi, buf_u = my_epi + C::EPI_BUF_BYTES,
-                       buf_o = my_epi + 2 * C::EPI_BUF_BYTES;
-#pragma unroll 1
-        for (int jb = 0; jb < 2; ++jb) {
-#pragma unroll 1
-          for (int h = 0; h < 2; ++h) {
-            uint32_t rg[32], ru[32];
-            ptx::tmem_ld_32x32(taddr + jb * 64 + h * 32, rg);
-            ptx::tmem_ld_32x32(taddr + 128 + jb * 64 + h * 32, ru);
-            ptx::tmem_ld_wait();
-            if (jb == 1 && h == 1) release_tmem();
-            if (!C::EPI_DIRECT && h == 0) {
-              if (lane == 0) ptx::tma_store_wait_read<0>();
-              __syncwarp();
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t pg[4], pu[4], po[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int c0 = i * 8 + e * 2;
-                if (ACC16) {
-                  // fp16 accumulators sit in the low half of each 32-bit column.
-                  const __half g0 = __ushort_as_half(static_cast<unsigned short>(rg[c0]));
-                  const __half g1 = __ushort_as_half(static_cast<unsigned short>(rg[c0 + 1]));
-                  const __half u0 = __ushort_as_half(static_cast<unsigned short>(ru[c0]));
-                  const __half u1 = __ushort_as_half(static_cast<unsigned short>(ru[c0 + 1]));
-                  const float gf0 = __half2float(g0), gf1 = __half2float(g1);
-                  const __half s0 = __float2half_rn(gf0 * sigmoid_f32(gf0));
-                  const __half s1 = __float2half_rn(gf1 * sigmoid_f32(gf1));
-                  const __half2 o = __hmul2(__halves2half2(u0, u1), __halves2half2(s0, s1));
-                  pg[e] = (rg[c0] & 0xFFFFu) | (rg[c0 + 1] << 16);
-                  pu[e] = (ru[c0] & 0xFFFFu) | (ru[c0 + 1] << 16);
-                  po[e] = *reinterpret_cast<const uint32_t*>(&o);
-                } else {
-                  const float g0 = __uint_as_float(rg[c0]), g1 = __uint_as_float(rg[c0 + 1]);
-                  const float u0 = __uint_as_float(ru[c0]), u1 = __uint_as_float(ru[c0 + 1]);
-                  const float s0 = round16<T>(g0 * sigmoid_f32(g0));
-                  const float s1 = round16<T>(g1 * sigmoid_f32(g1));
-                  pg[e] = pack2<T>(g0, g1);
-                  pu[e] = pack2<T>(u0, u1);
-                  po[e] = pack2<T>(u0 * s0, u1 * s1);
-                }
-              }
-              if (C::EPI_DIRECT) {
-                const int row = row0 + lane;
-                const int col = n0 + jb * 64 + h * 32 + i * 8;
-                if (row < p.M && col < p.N) {
-                  const size_t off = (static_cast<size_t>(row) * p.N + col) * 2;
-                  if (p.store_gu) {
-                    ptx::st_global_v4(static_cast<char*>(p.c0_ptr) + off, pg[0], pg[1], pg[2], pg[3]);
-                    ptx::st_global_v4(static_cast<char*>(p.c1_ptr) + off, pu[0], pu[1], pu[2], pu[3]);
-                  }
-                  ptx::st_global_v4(static_cast<char*>(p.c2_ptr) + off, po[0], po[1], po[2], po[3]);
-                }
-              } else {
-                const uint32_t off = row_off + (((h * 4 + i) ^ sw) << 4);
-                ptx::st_shared_v4(buf_g + off, pg[0], pg[1], pg[2], pg[3]);
-                ptx::st_shared_v4(buf_u + off, pu[0], pu[1], pu[2], pu[3]);
-                ptx::st_shared_v4(buf_o + off, po[0], po[1], po[2], po[3]);
-              }
-            }
-          }
-          if (C::EPI_DIRECT) continue;
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          const int col = n0 + jb * 64;
-          if (lane == 0 && row0 < p.M && col < p.N) {
-            if (p.store_gu) {
-              ptx::tma_store_2d(&p.c0, buf_g, col, row0);
-              ptx::tma_store_2d(&p.c1, buf_u, col, row0);
-            }
-            ptx::tma_store_2d(&p.c2, buf_o, col, row0);
-            ptx::tma_store_commit();
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int jb = 0; jb < 4; ++jb) {
-          uint32_t r0[32], r1[32];
-          ptx::tmem_ld_32x32(taddr + jb * 64, r0);
-          ptx::tmem_ld_32x32(taddr + jb * 64 + 32, r1);
-          ptx::tmem_ld_wait();
-          if (jb == 3) release_tmem();
-          if (!C::EPI_DIRECT) {
-            if (lane == 0) ptx::tma_store_wait_read<C::EPI_NBUF - 1>();
-            __syncwarp();
-          }
-          const uint32_t buf = my_epi + rb * C::EPI_BUF_BYTES;
-          const int col = (MODE == MODE_DX) ? (n0 + jb * 64) : (n0 + (jb & 1) * 64);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            uint32_t pk[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int c0 = (i & 3) * 8 + e * 2;
-              const uint32_t v0 = (i < 4) ? r0[c0] : r1[c0];
-              const uint32_t v1 = (i < 4) ? r0[c0 + 1] : r1[c0 + 1];
-              if (ACC16)
-                pk[e] = (v0 & 0xFFFFu) | (v1 << 16);
-              else
-                pk[e] = pack2<T>(__uint_as_float(v0), __uint_as_float(v1));
-            }
-            if (C::EPI_DIRECT) {
-              const int row = row0 + lane;
-              const int cc = col + i * 8;
-              if (row < p.M && cc < p.N) {
-                char* base = static_cast<char*>((MODE == MODE_DW && jb >= 2) ? p.c1_ptr : p.c0_ptr);
-                ptx::st_global_v4(base + (static_cast<size_t>(row) * p.N + cc) * 2, pk[0], pk[1], pk[2],
-                                  pk[3]);
-              }
-            } else {
-              ptx::st_shared_v4(buf + row_off + ((i ^ sw) << 4), pk[0], pk[1], pk[2], pk[3]);
-            }
-          }
-          if (C::EPI_DIRECT) continue;
-          ptx::fence_proxy_async_smem();
+      // Which accumulator regions this warp drains and which 64-column boxes of
+      // each.  NSUB==1: region `a`, boxes split between the two warps of a
+      // quadrant.  NSUB==2: with 8 warps one region per warp, with 4 both.
+      const int r_begin = (NSUB == 2) ? (kSplit == 2 ? chalf : 0) : a;
+      const int r_end = (NSUB == 2) ? (kSplit == 2 ? chalf + 1 : 2) : a + 1;
+      for (int r = r_begin; r < r_end; ++r) {
+        const uint32_t taddr = lane_base + r * C::BN;
+        const int rn0 = n0 + (NSUB == 2 ? r * C::REGION_N : 0);
+        auto release = [&]() {
+          ptx::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) {
-            if (row0 < p.M && col < p.N)
-              ptx::tma_store_2d((MODE == MODE_DW && jb >= 2) ? &p.c1 : &p.c0, buf, col, row0);
-            ptx::tma_store_commit();
+            if (CG == 2)
+              ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(r), 0));
+            else
+              ptx::mbar_arrive(tempty_bar(r));
           }
-          rb = (rb + 1 == C::EPI_NBUF) ? 0 : rb + 1;
+        };
+        const bool split = (NSUB == 1 && kSplit == 2);
+        if (FSW_DBG_SKIP_EPILOGUE) {
+          release();
+        } else if (MODE == MODE_FWD) {
+          const int jb0 = split ? chalf : 0;
+          const int jb1 = split ? chalf + 1 : 2;
+          drain_swiglu<C, T, ACC16>(p, e, taddr, rn0, jb0, jb1, release);
+        } else {
+          const int jb0 = split ? 2 * chalf : 0;
+          const int jb1 = split ? 2 * chalf + 2 : 4;
+          drain_plain<C, MODE, T, ACC16>(p, e, taddr, rn0, jb0, jb1, release);
         }
       }
-      a ^= 1;
-      if (a == 0) aph ^= 1u;
+      if (NSUB == 2) {
+        aph ^= 1u;
+      } else {
+        a ^= 1;
+        if (a == 0) aph ^= 1u;
+      }
     }
-    if (lane == 0) ptx::tma_store_wait_all<0>();
-    __syncwarp();
   }
 
   // ======================= teardown =======================
+  __syncwarp();
   ptx::tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag != 0u) {
@@ -514,6 +620,10 @@ __global__ void __launch_bounds__(192, 1) gemm_kernel(const __grid_constant__ Ge
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc<CG>(tmem_base, C::TMEM_COLS);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0 && p.clk_probe != nullptr) {
+    p.clk_probe[0] = static_cast<unsigned long long>(clock64() - probe_c0);
+    p.clk_probe[1] = ptx::globaltimer_ns() - probe_t0;
   }
 }
 

@@ -232,6 +232,15 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
                : "memory");
 }
 
+// 16-byte shared-memory load.
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c,
+                                             uint32_t& d) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+               : "r"(addr)
+               : "memory");
+}
+
 // 16-byte global store.
 __device__ __forceinline__ void st_global_v4(void* addr, uint32_t a, uint32_t b, uint32_t c,
                                              uint32_t d) {
