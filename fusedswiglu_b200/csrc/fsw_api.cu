@@ -594,4 +594,48 @@ int fsw_backward(const void* dout, const void* x, const void* w_gate, const void
                          stream);
 }
 
+// ------------------------------------------------- backward without allocation --
+// Scratch for fsw_backward_static_scratch: dg and du, each up to
+// FSW_STATIC_SCRATCH_ELEMS 16-bit elements, 256-byte aligned.  The array lives in
+// the library image, so every GPU that loads the library holds these 16 MiB until
+// the process exits.  In host code `g_static_scratch` is only a handle for
+// cudaGetSymbolAddress; the device address is resolved once per device below.
+static __device__ __align__(256) unsigned char g_static_scratch[2ull * FSW_STATIC_SCRATCH_ELEMS * 2ull];
+static unsigned char* g_static_scratch_ptr[fsw::kMaxDevices] = {};
+
+int fsw_backward_static_scratch(const void* dout, const void* x, const void* w_gate,
+                                const void* w_up, const void* g, const void* u, void* dx,
+                                void* dw_gate, void* dw_up, int64_t T, int64_t dm, int64_t di,
+                                int dtype, int accum, void* stream) {
+  int rc = check_common(T, dm, di, dtype, accum);
+  if (rc != FSW_OK) return rc;
+  if (T * di > (int64_t)FSW_STATIC_SCRATCH_ELEMS)
+    return fail(FSW_EINVAL,
+                "T*d_intermediate = %lld exceeds the built-in scratch of %lld elements per tensor; "
+                "use fsw_backward with caller-provided scratch for this size",
+                (long long)(T * di), (long long)FSW_STATIC_SCRATCH_ELEMS);
+  int dev = 0;
+  FSW_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(FSW_EINVAL, "device index %d out of range", dev);
+  unsigned char* base = nullptr;
+  {
+    // First call on this device: turn the symbol into this device's address.
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+      void* sp = nullptr;
+      FSW_CUDA(cudaGetSymbolAddress(&sp, g_static_scratch));
+      g_static_scratch_ptr[dev] = static_cast<unsigned char*>(sp);
+    }
+    base = g_static_scratch_ptr[dev];
+  }
+  // dg first, du after it on the next 256-byte boundary.  Both are fully
+  // overwritten by the elementwise step before the GEMMs read them, so nothing
+  // needs clearing between calls.
+  const size_t dg_bytes = ((size_t)(T * di) * 2 + 255) & ~(size_t)255;
+  void* dg = base;
+  void* du = base + dg_bytes;
+  return fsw_backward(dout, x, w_gate, w_up, g, u, dg, du, dx, dw_gate, dw_up, T, dm, di, dtype,
+                      accum, stream);
+}
+
 }  // extern "C"

@@ -87,6 +87,39 @@ int fsw_backward(const void* dout, const void* x, const void* w_gate, const void
                  void* dw_gate, void* dw_up, int64_t T, int64_t dm, int64_t di, int dtype,
                  int accum, void* stream);
 
+/*
+ * fsw_backward for callers that have no scratch memory to give and may not
+ * allocate any.  (No counterpart in the reference, whose launchers allocate
+ * fresh dg/du tensors on every call.)
+ *
+ * Some hosts of this library cannot call cudaMalloc at the point where they need
+ * the backward: an inference/training runtime whose device memory is planned up
+ * front and handed out from a fixed arena, a plugin's enqueue hook that is
+ * forbidden to allocate, or a latency-critical loop that cannot afford the
+ * device-wide synchronisation cudaMalloc and cudaFree imply.  For them the dg/du
+ * scratch lives in a fixed array inside the library instead of in an argument:
+ *
+ *   - limit: T * di <= FSW_STATIC_SCRATCH_ELEMS (4 Mi elements; 16 MiB for dg and
+ *     du together, held by every GPU that loads the library until the process
+ *     exits).  Larger problems get FSW_EINVAL with a message naming the limit;
+ *     use fsw_backward with your own scratch for those;
+ *   - the call allocates nothing: no cudaMalloc/cudaFree, no allocating library
+ *     routine.  Inputs and outputs are still the caller's buffers;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current).  Make that first call
+ *     before starting any stream capture;
+ *   - every call on a device shares the one array.  Its contents after a call are
+ *     that call's dg/du; the next call overwrites all it reads, so nothing has to
+ *     be cleared.  Two calls that overlap on the GPU (different streams, or
+ *     different host threads) race on it: serialise them.
+ * Arguments and results are otherwise those of fsw_backward.
+ */
+#define FSW_STATIC_SCRATCH_ELEMS (4 * 1024 * 1024)
+int fsw_backward_static_scratch(const void* dout, const void* x, const void* w_gate,
+                                const void* w_up, const void* g, const void* u, void* dx,
+                                void* dw_gate, void* dw_up, int64_t T, int64_t dm, int64_t di,
+                                int dtype, int accum, void* stream);
+
 /* Message for the last non-zero return on the calling thread ("" if none). */
 const char* fsw_last_error(void);
 
