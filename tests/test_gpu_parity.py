@@ -206,6 +206,53 @@ def test_fp16_fast_accum_against_fp32_accum(d_model):
         assert rep["rel_fro"] < BFLOAT16_MAX_TOL, (k, rep)
 
 
+@pytest.mark.parametrize("d_model", [1024, 2048, 4096, 8192])
+def test_fp16_fast_accum_sweep_at_full_size(d_model):
+    """The fp16 sweep of the benchmark configurations: x (4, 2048, d_model),
+    d_intermediate = 3*d_model, weights N(0, 1/d_model), dout = 0.1*randn; the
+    fp16-accumulator run is compared with the fp32-accumulate run, per tensor."""
+    from fusedswiglu_b200 import _launch
+
+    T, di = 4 * 2048, 3 * d_model
+    gen = torch.Generator(device="cuda").manual_seed(d_model)
+    mk = lambda *s: torch.randn(*s, device="cuda", dtype=torch.float16, generator=gen)
+    x, wg, wu = mk(T, d_model), mk(d_model, di) / math.sqrt(d_model), mk(d_model, di) / math.sqrt(d_model)
+    dout = 0.1 * mk(T, di)
+    res = {}
+    for fast in (False, True):
+        out, g, u = _launch.forward(x, wg, wu, fast_accum=fast)
+        dg, du = _launch.gate_grad(dout, g, u)
+        dx = _launch.grad_input(dg, du, wg, wu)
+        dwg, dwu = _launch.grad_weights(x, dg, du, fast_accum=fast)
+        res[fast] = {"out": out, "dx": dx, "dw_gate": dwg, "dw_up": dwu}
+        del g, u, dg, du
+    for k in ("out", "dx", "dw_gate", "dw_up"):
+        a, b = res[True][k].float(), res[False][k].float()
+        assert torch.all(torch.isfinite(a)), (d_model, k)
+        e = (torch.linalg.norm(a - b) / torch.linalg.norm(b)).item()
+        print(f"fp16 sweep d_model={d_model} {k}: rel_fro={e:.3e} max_abs={(a - b).abs().max().item():.3e}")
+        assert e < BFLOAT16_MAX_TOL, (d_model, k, e)
+
+
+def test_llama3_70b_shape_forward_only():
+    """The largest configuration (16 x 4096 tokens, d_model 8192, d_intermediate
+    28672) runs forward-only on one GPU: sampled rows against float64."""
+    from fusedswiglu_b200 import _launch
+
+    T, dm, di = 16 * 4096, 8192, 28672
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(T, dm, device="cuda", dtype=torch.bfloat16, generator=gen)
+    wg = torch.randn(dm, di, device="cuda", dtype=torch.bfloat16, generator=gen) / math.sqrt(dm)
+    wu = torch.randn(dm, di, device="cuda", dtype=torch.bfloat16, generator=gen) / math.sqrt(dm)
+    out, _, _ = _launch.forward(x, wg, wu, save_activations=False)
+    rows = torch.randint(0, T, (32,), device="cuda")
+    g_ref = x[rows].double() @ wg.double()
+    u_ref = x[rows].double() @ wu.double()
+    assert rel_error(out[rows], torch.nn.functional.silu(g_ref) * u_ref) < EXPECTED_BF16
+    # last tile rows and columns are written
+    assert torch.all(torch.isfinite(out[-1].float())) and out[-1].abs().sum() > 0
+
+
 def test_fast_accum_function_matches_reference_semantics():
     from fused_swiglu import FastAccumFusedSwiGLU
     from fused_swiglu.kernels.kernels_fp16 import fused_swiglu_fwd
