@@ -39,6 +39,8 @@ struct Options {
   int64_t cta_group = 2;
   int64_t nsub = 2;  // accumulator regions per tile (2 needs cta_group 2)
   int64_t group_m = 8;
+  int64_t l2_a = 0, l2_b = 0;    // L2 eviction priority of A / B operand loads (0/1/2)
+  int64_t ew_blocks_per_sm = 32;  // grid cap of the elementwise kernel, per SM
   // Debug overrides of the UMMA shared-memory descriptor fields (0 = built-in).
   int64_t k_lbo = 0, k_sbo = 0, k_kadv = 0;
   int64_t mn_lbo = 0, mn_sbo = 0, mn_kadv = 0;
@@ -48,7 +50,7 @@ static Options g_opt;
 // Status word the kernels write when a bounded wait gives up.
 __device__ uint32_t g_status_word;
 // SM cycles and nanoseconds that CTA 0 of the last GEMM launch was resident.
-__device__ unsigned long long g_clk_probe[2];
+__device__ unsigned long long g_clk_probe[8];
 
 // ------------------------------------------------------------ device cache --
 constexpr int kMaxDevices = 64;
@@ -274,6 +276,8 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   p.group_m = (int)g_opt.group_m < 1 ? 1 : (int)g_opt.group_m;
   p.status = d->status;
   p.clk_probe = d->clk_probe;
+  p.l2_a = (int)g_opt.l2_a;
+  p.l2_b = (int)g_opt.l2_b;
   const int a_major = (MODE == MODE_DW) ? MAJOR_MN : MAJOR_K;
   const int b_major = (MODE == MODE_DX) ? MAJOR_K : MAJOR_MN;
   fill_operand_desc(a_major, &p.a_desc, &p.a_kadv);
@@ -319,6 +323,35 @@ __device__ __forceinline__ float to_f32<__half>(__half v) {
   return __half2float(v);
 }
 
+// 16-byte streaming load / store: every operand is touched once per launch.
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm("ld.global.nc.L1::no_allocate.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void gate_grad_vec(const uint4& vd, const uint4& vg, const uint4& vu,
+                                              uint4& odg, uint4& odu) {
+  const T* pd = reinterpret_cast<const T*>(&vd);
+  const T* pg = reinterpret_cast<const T*>(&vg);
+  const T* pu = reinterpret_cast<const T*>(&vu);
+  uint32_t* wdg = reinterpret_cast<uint32_t*>(&odg);
+  uint32_t* wdu = reinterpret_cast<uint32_t*>(&odu);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float dg0, du0, dg1, du1;
+    gate_grad_one<T>(to_f32(pd[2 * e]), to_f32(pg[2 * e]), to_f32(pu[2 * e]), dg0, du0);
+    gate_grad_one<T>(to_f32(pd[2 * e + 1]), to_f32(pg[2 * e + 1]), to_f32(pu[2 * e + 1]), dg1, du1);
+    wdg[e] = pack2<T>(dg0, dg1);
+    wdu[e] = pack2<T>(du0, du1);
+  }
+}
+
+constexpr int kGateGradUnroll = 4;  // 16-byte vectors per thread and tensor in flight
+
 template <typename T>
 __global__ void __launch_bounds__(256) gate_grad_kernel(const T* __restrict__ dout,
                                                        const T* __restrict__ g,
@@ -326,25 +359,32 @@ __global__ void __launch_bounds__(256) gate_grad_kernel(const T* __restrict__ do
                                                        T* __restrict__ du, int64_t numel) {
   const int64_t nvec = numel >> 3;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
-    const uint4 vd = __ldg(reinterpret_cast<const uint4*>(dout) + v);
-    const uint4 vg = __ldg(reinterpret_cast<const uint4*>(g) + v);
-    const uint4 vu = __ldg(reinterpret_cast<const uint4*>(u) + v);
-    const T* pd = reinterpret_cast<const T*>(&vd);
-    const T* pg = reinterpret_cast<const T*>(&vg);
-    const T* pu = reinterpret_cast<const T*>(&vu);
-    uint4 odg, odu;
-    uint32_t* wdg = reinterpret_cast<uint32_t*>(&odg);
-    uint32_t* wdu = reinterpret_cast<uint32_t*>(&odu);
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint4* d4 = reinterpret_cast<const uint4*>(dout);
+  const uint4* g4 = reinterpret_cast<const uint4*>(g);
+  const uint4* u4 = reinterpret_cast<const uint4*>(u);
+  int64_t v = tid;
+  // main loop: kGateGradUnroll independent vectors per thread, all loads issued
+  // before the first use
+  for (; v + (kGateGradUnroll - 1) * stride < nvec; v += kGateGradUnroll * stride) {
+    uint4 vd[kGateGradUnroll], vg[kGateGradUnroll], vu[kGateGradUnroll];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float dg0, du0, dg1, du1;
-      gate_grad_one<T>(to_f32(pd[2 * e]), to_f32(pg[2 * e]), to_f32(pu[2 * e]), dg0, du0);
-      gate_grad_one<T>(to_f32(pd[2 * e + 1]), to_f32(pg[2 * e + 1]), to_f32(pu[2 * e + 1]), dg1,
-                       du1);
-      wdg[e] = pack2<T>(dg0, dg1);
-      wdu[e] = pack2<T>(du0, du1);
+    for (int j = 0; j < kGateGradUnroll; ++j) {
+      vd[j] = ld_stream(d4 + v + j * stride);
+      vg[j] = ld_stream(g4 + v + j * stride);
+      vu[j] = ld_stream(u4 + v + j * stride);
     }
+#pragma unroll
+    for (int j = 0; j < kGateGradUnroll; ++j) {
+      uint4 odg, odu;
+      gate_grad_vec<T>(vd[j], vg[j], vu[j], odg, odu);
+      reinterpret_cast<uint4*>(dg)[v + j * stride] = odg;
+      reinterpret_cast<uint4*>(du)[v + j * stride] = odu;
+    }
+  }
+  for (; v < nvec; v += stride) {
+    uint4 odg, odu;
+    gate_grad_vec<T>(ld_stream(d4 + v), ld_stream(g4 + v), ld_stream(u4 + v), odg, odu);
     reinterpret_cast<uint4*>(dg)[v] = odg;
     reinterpret_cast<uint4*>(du)[v] = odu;
   }
@@ -412,6 +452,12 @@ int fsw_set_option(const char* name, int64_t value) {
   } else if (!strcmp(name, "group_m")) {
     if (value < 1 || value > (1 << 20)) return fail(FSW_EINVAL, "group_m must be >= 1");
     g_opt.group_m = value;
+  } else if (!strcmp(name, "l2_a") || !strcmp(name, "l2_b")) {
+    if (value < 0 || value > 2) return fail(FSW_EINVAL, "%s must be 0, 1 or 2", name);
+    (name[3] == 'a' ? g_opt.l2_a : g_opt.l2_b) = value;
+  } else if (!strcmp(name, "ew_blocks_per_sm")) {
+    if (value < 1 || value > 64) return fail(FSW_EINVAL, "ew_blocks_per_sm must be in [1, 64]");
+    g_opt.ew_blocks_per_sm = value;
   } else if (!strcmp(name, "k_lbo")) {
     g_opt.k_lbo = value;
   } else if (!strcmp(name, "k_sbo")) {
@@ -435,6 +481,9 @@ int64_t fsw_get_option(const char* name) {
   if (!strcmp(name, "cta_group")) return g_opt.cta_group;
   if (!strcmp(name, "group_m")) return g_opt.group_m;
   if (!strcmp(name, "nsub")) return g_opt.nsub;
+  if (!strcmp(name, "ew_blocks_per_sm")) return g_opt.ew_blocks_per_sm;
+  if (!strcmp(name, "l2_a")) return g_opt.l2_a;
+  if (!strcmp(name, "l2_b")) return g_opt.l2_b;
   if (!strcmp(name, "k_lbo")) return g_opt.k_lbo;
   if (!strcmp(name, "k_sbo")) return g_opt.k_sbo;
   if (!strcmp(name, "k_kadv")) return g_opt.k_kadv;
@@ -449,6 +498,15 @@ int64_t fsw_get_option(const char* name) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
     if (cudaMemcpy(v, d->clk_probe, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     return v[1] ? (int64_t)(v[0] * 1000000ull / v[1]) : -1;
+  }
+  if (!strncmp(name, "probe", 5) && name[5] >= '0' && name[5] <= '7' && name[6] == 0) {
+    // Raw diagnostic counters of the last GEMM launch (see FSW_PROFILE); synchronises.
+    DeviceInfo* d = nullptr;
+    if (ensure_device(&d) != FSW_OK) return -1;
+    unsigned long long v[8] = {};
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpy(v, d->clk_probe, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return (int64_t)v[name[5] - '0'];
   }
   if (!strcmp(name, "max_pairs") || !strcmp(name, "sm_count") || !strcmp(name, "stages")) {
     // facts about the current device (initialises it on first use)
@@ -505,7 +563,7 @@ int fsw_backward_elementwise(const void* dout, const void* g, const void* u, voi
   if (rc != FSW_OK) return rc;
   const int64_t nvec = numel >> 3;
   int64_t blocks = (nvec + 255) / 256;
-  const int64_t cap = (int64_t)d->sm_count * 16;
+  const int64_t cap = (int64_t)d->sm_count * (g_opt.ew_blocks_per_sm > 0 ? g_opt.ew_blocks_per_sm : 32);
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

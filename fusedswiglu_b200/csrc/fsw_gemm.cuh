@@ -59,6 +59,7 @@ struct GemmParams {
   int num_m_tiles, num_n_tiles, group_m;
   int num_k_blocks;        // 64-wide K blocks per product
   int store_gu;            // MODE_FWD: also write g and u
+  int l2_a, l2_b;          // L2 eviction priority of A / B loads: 0 normal, 1 first, 2 last
   uint32_t* status;        // device status word (0 = ok)
   void *c0_ptr, *c1_ptr, *c2_ptr;  // outputs (see the mode table above); row stride N
   unsigned long long* clk_probe;   // [2]: SM cycles and nanoseconds CTA 0 was resident
@@ -81,6 +82,12 @@ constexpr int kSmemBudget = 232448;  // 227 KB opt-in limit per CTA
 #endif
 #ifndef FSW_DBG_SKIP_B_LOADS
 #define FSW_DBG_SKIP_B_LOADS 0
+#endif
+// Cycle accounting (diagnostic builds only): the MMA thread and one epilogue warp
+// of CTA 0 add up the SM cycles they spend in each wait and write them to
+// clk_probe[2..7].
+#ifndef FSW_PROFILE
+#define FSW_PROFILE 0
 #endif
 
 template <int MODE, int CG, int NSUB>
@@ -422,6 +429,8 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      const uint64_t pol_a = ptx::make_l2_policy(p.l2_a);
+      const uint64_t pol_b = ptx::make_l2_policy(p.l2_b);
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
         int m_tile, n_tile;
         decode_tile(t, p, m_tile, n_tile);
@@ -439,19 +448,25 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
             if (cta_rank == 0)
               ptx::mbar_arrive_expect_tx(full_bar(s),
                                          CG * (FSW_DBG_SKIP_B_LOADS ? C::A_BYTES : C::STAGE_BYTES));
-            auto load = [&](uint32_t dst, const CUtensorMap* tm, int x, int y) {
+            auto load_pol = [&](uint32_t dst, const CUtensorMap* tm, int x, int y, uint64_t pol) {
               if (CG == 2)
-                ptx::tma_load_2d_pair(dst, tm, fb, x, y);
+                ptx::tma_load_2d_pair(dst, tm, fb, x, y, pol);
               else
-                ptx::tma_load_2d(dst, tm, fb, x, y);
+                ptx::tma_load_2d(dst, tm, fb, x, y, pol);
+            };
+            auto load_a = [&](uint32_t dst, const CUtensorMap* tm, int x, int y) {
+              load_pol(dst, tm, x, y, pol_a);
+            };
+            auto load = [&](uint32_t dst, const CUtensorMap* tm, int x, int y) {
+              load_pol(dst, tm, x, y, pol_b);
             };
             // ---- A tile: 128 rows x 64 k
             if (C::A_MAJOR == MAJOR_K) {
-              load(a_dst, (MODE == MODE_DX && seg == 1) ? &p.a1 : &p.a0, k0, m0);
+              load_a(a_dst, (MODE == MODE_DX && seg == 1) ? &p.a1 : &p.a0, k0, m0);
             } else {
 #pragma unroll
               for (int c = 0; c < C::BM / 64; ++c)
-                load(a_dst + c * C::CHUNK_BYTES, &p.a0, m0 + c * 64, k0);
+                load_a(a_dst + c * C::CHUNK_BYTES, &p.a0, m0 + c * 64, k0);
             }
             // ---- B: one SUB_ROWS x 64 sub-tile per accumulator region
             if (!FSW_DBG_SKIP_B_LOADS) {
@@ -487,6 +502,7 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
       int s = 0, a = 0;
       uint32_t ph = 0, aph = 0;
       bool ok = true;
+      long long prof_full = 0, prof_tempty = 0, prof_t0 = 0;
       auto commit = [&](uint32_t bar) {
         if (CG == 2)
           ptx::mma_commit_pair(bar, 3);
@@ -501,7 +517,9 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
         }
         const int iters = C::NSEG * num_kb;
         for (int it = 0; it < iters; ++it) {
+          if (FSW_PROFILE) prof_t0 = clock64();
           if (!FSW_DBG_SKIP_LOADS) ok = bounded_wait_thread(full_bar(s), ph, ctl, WAIT_MMA_FULL);
+          if (FSW_PROFILE) prof_full += clock64() - prof_t0;
           if (!ok) break;
           ptx::tc_fence_after_sync();
           const uint32_t a_addr = smem_base + s * C::STAGE_BYTES;
@@ -510,7 +528,9 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
           for (int r = 0; r < NSUB; ++r) {
             if (NSUB == 2 && it == 0) {
               // both regions belong to this tile; region r must have been drained
+              if (FSW_PROFILE) prof_t0 = clock64();
               ok = bounded_wait_thread(tempty_bar(r), aph ^ 1u, ctl, WAIT_MMA_TMEM_EMPTY);
+              if (FSW_PROFILE) prof_tempty += clock64() - prof_t0;
               if (!ok) break;
               ptx::tc_fence_after_sync();
             }
@@ -540,6 +560,10 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
           if (a == 0) aph ^= 1u;
         }
       }
+      if (FSW_PROFILE && blockIdx.x == 0 && p.clk_probe != nullptr) {
+        p.clk_probe[2] = prof_full;
+        p.clk_probe[3] = prof_tempty;
+      }
     }
   } else {
     // ======================= epilogue =======================
@@ -553,12 +577,20 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
     int a = 0;
     uint32_t aph = 0;
     bool ok = true;
+    long long prof_wait = 0, prof_drain = 0, prof_t0 = 0, prof_tiles = 0;
     for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
       int m_tile, n_tile;
       decode_tile(t, p, m_tile, n_tile);
       e.row0 = m_tile * C::TILE_M + cta_rank * C::BM + q * 32;
       const int n0 = n_tile * C::TILE_N;
+      if (FSW_PROFILE) prof_t0 = clock64();
       ok = bounded_wait_warp(tfull_bar(NSUB == 2 ? 0 : a), aph, ctl, WAIT_EPI_TMEM_FULL);
+      if (FSW_PROFILE) {
+        const long long now = clock64();
+        prof_wait += now - prof_t0;
+        prof_t0 = now;
+        ++prof_tiles;
+      }
       if (!ok) break;
       ptx::tc_fence_after_sync();
       const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
@@ -594,12 +626,18 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
           drain_plain<C, MODE, T, ACC16>(p, e, taddr, rn0, jb0, jb1, release);
         }
       }
+      if (FSW_PROFILE) prof_drain += clock64() - prof_t0;
       if (NSUB == 2) {
         aph ^= 1u;
       } else {
         a ^= 1;
         if (a == 0) aph ^= 1u;
       }
+    }
+    if (FSW_PROFILE && blockIdx.x == 0 && warp == 2 && lane == 0 && p.clk_probe != nullptr) {
+      p.clk_probe[4] = prof_wait;
+      p.clk_probe[5] = prof_drain;
+      p.clk_probe[6] = prof_tiles;
     }
   }
 
