@@ -46,7 +46,7 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 NCU_TRAFFIC_BYTES = {}
 
 CLOCK_QUERY = (
-    "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    "timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
     "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
     "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 )
@@ -93,14 +93,16 @@ class ClockSampler:
         os.close(fd)
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", self.gpu_id],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL,
             )
         except OSError:
             self.proc = None
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summarise the samples; with a (t_begin, t_end) host-time window only the
+        samples taken inside it count (falling back to all if none did)."""
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
@@ -115,6 +117,22 @@ class ClockSampler:
             if len(f) >= 9:
                 rows.append(f)
         os.unlink(self.path)
+        if t_begin is not None and t_end is not None:
+            import datetime
+
+            inside = []
+            for r in rows:
+                try:
+                    ts = datetime.datetime.strptime(r[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                except ValueError:
+                    continue
+                if t_begin <= ts <= t_end:
+                    inside.append(r)
+            if inside:
+                rows = inside
+                out["window"] = "timed region"
+            else:
+                out["window"] = "warm-up and timed region (no sample fell inside the timed region)"
         if not rows:
             return out
         sm = sorted(float(r[1]) for r in rows if r[1].replace(".", "").isdigit())
@@ -240,8 +258,12 @@ def run_ours(args):
         if marks: marks[2].record()
         dx = _launch.grad_input(dg, du, wg, wu)
         if marks: marks[3].record()
-        work = dist.all_reduce(dx, async_op=True) if world > 1 else None
-        dwg, dwu = _launch.grad_weights(x2d, dg, du)
+        if world > 1:
+            work = dist.all_reduce(dx, async_op=True)
+            dwg, dwu = parallel._CudaBackend.grad_weights_beside_collective(x2d, dg, du)
+        else:
+            work = None
+            dwg, dwu = _launch.grad_weights(x2d, dg, du)
         if marks: marks[4].record()
         if work is not None:
             work.wait()
@@ -277,9 +299,8 @@ def run_ours(args):
                           "status": _lib.device_status()}), flush=True)
         return
 
-    for _ in range(W):
-        step()
-    barrier()
+    # The clock sampler runs from the warm-up on (same workload), so that short
+    # timed regions still collect samples under load.
     props = torch.cuda.get_device_properties(dev)
     gpu_id = str(getattr(props, "uuid", local_rank))
     if not gpu_id.startswith("GPU-") and len(gpu_id) > 8:
@@ -287,14 +308,20 @@ def run_ours(args):
     sampler = ClockSampler(gpu_id if rank == 0 else str(local_rank))
     if rank == 0:
         sampler.start()
+        time.sleep(0.3)
+    for _ in range(W):
+        step()
+    barrier()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    wall0 = time.time()
     t_start.record()
     for i in range(K):
         step(ev[i])
     t_end.record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    wall1 = time.time()
+    clocks = sampler.stop(wall0, wall1) if rank == 0 else None
     total_ms = t_start.elapsed_time(t_end)
     per_kernel_ms = [sum(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(K)) / K for j in range(4)]
     if world > 1:
@@ -411,6 +438,7 @@ def run_ours(args):
         "config": {"workload": args.workload, "bs": bs, "sq": sq, "d_model": dm, "d_intermediate": di,
                    "parallelism": f"column-parallel d_intermediate x{world}" if world > 1 else "single GPU",
                    "l2": "inputs larger than L2 (activations and weights exceed 126 MB); no flush",
+                   "comm_sms_reserved_during_dw": parallel.COMM_SMS if world > 1 else 0,
                    "accumulate": "fp32", "cta_group": _lib.get_option("cta_group"),
                    "group_m": _lib.get_option("group_m")},
         "frac_of_nominal_bf16_peak": value / (NOMINAL_BF16_TFLOPS * world),

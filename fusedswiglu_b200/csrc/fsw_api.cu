@@ -39,6 +39,7 @@ struct Options {
   int64_t cta_group = 2;
   int64_t nsub = 2;  // accumulator regions per tile (2 needs cta_group 2)
   int64_t group_m = 8;
+  int64_t gemm_max_sms = 0;      // cap on SMs a GEMM launch occupies (0 = all of them)
   int64_t l2_a = 0, l2_b = 0;    // L2 eviction priority of A / B operand loads (0/1/2)
   int64_t ew_blocks_per_sm = 32;  // grid cap of the elementwise kernel, per SM
   // Debug overrides of the UMMA shared-memory descriptor fields (0 = built-in).
@@ -156,17 +157,18 @@ static int ensure_device(DeviceInfo** out) {
 
 // ------------------------------------------------------------- tensor maps --
 // Row-major (outer, inner) array of 16-bit elements; box = box_outer rows of 64
-// elements (128 bytes), 128-byte swizzle.
+// elements (128 bytes, 128-byte swizzle) or of 32 elements (64 bytes, 64-byte swizzle).
 static int make_map(CUtensorMap* m, const void* ptr, int dtype, uint64_t inner, uint64_t outer,
-                    uint32_t box_outer, const char* what) {
+                    uint32_t box_outer, const char* what, uint32_t box_inner = 64) {
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {inner * 2};
-  cuuint32_t box[2] = {64, box_outer};
+  cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode(
       m, dtype == FSW_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
       const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      box_inner == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(FSW_ECUDA, "cuTensorMapEncodeTiled(%s: inner=%llu outer=%llu box_outer=%u) -> %d",
@@ -287,12 +289,16 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   if (tiles <= 0) return FSW_OK;
   if (tiles >= (1ll << 31)) return fail(FSW_EINVAL, "too many tiles");
   cudaError_t e;
+  int avail_sms = d->sm_count;
+  if (g_opt.gemm_max_sms > 0 && g_opt.gemm_max_sms < avail_sms) avail_sms = (int)g_opt.gemm_max_sms;
   if (cg == 2) {
-    const int pairs = (int)(tiles < d->max_pairs ? tiles : d->max_pairs);
+    int max_pairs = d->max_pairs < avail_sms / 2 ? d->max_pairs : avail_sms / 2;
+    if (max_pairs < 1) max_pairs = 1;
+    const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
     e = (nsub == 2) ? launch_cg<MODE, 2, 2>(p, 2 * pairs, dtype, acc16, st)
                     : launch_cg<MODE, 2, 1>(p, 2 * pairs, dtype, acc16, st);
   } else {
-    const int ctas = (int)(tiles < d->sm_count ? tiles : d->sm_count);
+    const int ctas = (int)(tiles < avail_sms ? tiles : avail_sms);
     e = launch_cg<MODE, 1, 1>(p, ctas, dtype, acc16, st);
   }
   if (e != cudaSuccess) return fail(FSW_ECUDA, "kernel launch failed: %s", cudaGetErrorString(e));
@@ -306,8 +312,9 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
 template <typename T>
 __device__ __forceinline__ void gate_grad_one(float dout, float g, float u, float& dg, float& du) {
   const float sg = sigmoid_f32(g);
-  const float silu = round16<T>(g * sg);
-  const float dsilu = round16<T>(sg + g * sg * (1.0f - sg));
+  const float silu_f = g * sg;
+  const float silu = round16<T>(silu_f);
+  const float dsilu = round16<T>(fmaf(silu_f, 1.0f - sg, sg));  // sg + g*sg*(1-sg)
   du = round16<T>(dout * silu);
   dg = round16<T>(round16<T>(dout * u) * dsilu);
 }
@@ -332,21 +339,26 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
   return v;
 }
 
+// One 16-byte vector (8 elements).  Only g is widened to fp32 (sigmoid); the
+// products are packed 16-bit multiplies, each rounding once like the fp32 form.
 template <typename T>
 __device__ __forceinline__ void gate_grad_vec(const uint4& vd, const uint4& vg, const uint4& vu,
                                               uint4& odg, uint4& odu) {
-  const T* pd = reinterpret_cast<const T*>(&vd);
-  const T* pg = reinterpret_cast<const T*>(&vg);
-  const T* pu = reinterpret_cast<const T*>(&vu);
+  const uint32_t* wd = reinterpret_cast<const uint32_t*>(&vd);
+  const uint32_t* wg = reinterpret_cast<const uint32_t*>(&vg);
+  const uint32_t* wu = reinterpret_cast<const uint32_t*>(&vu);
   uint32_t* wdg = reinterpret_cast<uint32_t*>(&odg);
   uint32_t* wdu = reinterpret_cast<uint32_t*>(&odu);
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
-    float dg0, du0, dg1, du1;
-    gate_grad_one<T>(to_f32(pd[2 * e]), to_f32(pg[2 * e]), to_f32(pu[2 * e]), dg0, du0);
-    gate_grad_one<T>(to_f32(pd[2 * e + 1]), to_f32(pg[2 * e + 1]), to_f32(pu[2 * e + 1]), dg1, du1);
-    wdg[e] = pack2<T>(dg0, dg1);
-    wdu[e] = pack2<T>(du0, du1);
+    float g0, g1;
+    unpack2<T>(wg[e], g0, g1);
+    const float s0 = sigmoid_f32(g0), s1 = sigmoid_f32(g1);
+    const float silu0 = g0 * s0, silu1 = g1 * s1;
+    const uint32_t silu = pack2<T>(silu0, silu1);
+    const uint32_t dsilu = pack2<T>(fmaf(silu0, 1.0f - s0, s0), fmaf(silu1, 1.0f - s1, s1));
+    wdu[e] = mul2<T>(wd[e], silu);
+    wdg[e] = mul2<T>(mul2<T>(wd[e], wu[e]), dsilu);
   }
 }
 
@@ -452,6 +464,9 @@ int fsw_set_option(const char* name, int64_t value) {
   } else if (!strcmp(name, "group_m")) {
     if (value < 1 || value > (1 << 20)) return fail(FSW_EINVAL, "group_m must be >= 1");
     g_opt.group_m = value;
+  } else if (!strcmp(name, "gemm_max_sms")) {
+    if (value < 0) return fail(FSW_EINVAL, "gemm_max_sms must be >= 0");
+    g_opt.gemm_max_sms = value;
   } else if (!strcmp(name, "l2_a") || !strcmp(name, "l2_b")) {
     if (value < 0 || value > 2) return fail(FSW_EINVAL, "%s must be 0, 1 or 2", name);
     (name[3] == 'a' ? g_opt.l2_a : g_opt.l2_b) = value;
@@ -482,6 +497,7 @@ int64_t fsw_get_option(const char* name) {
   if (!strcmp(name, "group_m")) return g_opt.group_m;
   if (!strcmp(name, "nsub")) return g_opt.nsub;
   if (!strcmp(name, "ew_blocks_per_sm")) return g_opt.ew_blocks_per_sm;
+  if (!strcmp(name, "gemm_max_sms")) return g_opt.gemm_max_sms;
   if (!strcmp(name, "l2_a")) return g_opt.l2_a;
   if (!strcmp(name, "l2_b")) return g_opt.l2_b;
   if (!strcmp(name, "k_lbo")) return g_opt.k_lbo;
@@ -539,6 +555,9 @@ int fsw_forward(const void* x, const void* w_gate, const void* w_up, void* out, 
   p.a1 = p.a0;
   if ((rc = make_map(&p.b0, w_gate, dtype, di, dm, 64, "w_gate")) != FSW_OK) return rc;
   if ((rc = make_map(&p.b1, w_up, dtype, di, dm, 64, "w_up")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.sg, g ? g : out, dtype, di, T, 32, "g (store)", 32)) != FSW_OK) return rc;
+  if ((rc = make_map(&p.su, u ? u : out, dtype, di, T, 32, "u (store)", 32)) != FSW_OK) return rc;
+  if ((rc = make_map(&p.so, out, dtype, di, T, 32, "out (store)", 32)) != FSW_OK) return rc;
   p.M = (int)T;
   p.N = (int)di;
   p.num_k_blocks = (int)((dm + 63) / 64);

@@ -23,7 +23,9 @@
 //
 // Warp roles: warp 0 = TMA producer (one thread), warp 1 = TMEM owner and MMA
 // issuer (one thread), warps 2.. = epilogue (TMEM -> registers -> 16-bit results
-// -> per-warp shared-memory transpose -> row-coalesced 16-byte global stores).
+// -> per-warp swizzled shared-memory buffer -> global memory; the plain GEMMs read
+// the buffer back for row-coalesced 16-byte stores, the SwiGLU epilogue hands it to
+// TMA stores).
 //
 // Every mbarrier wait is bounded: after kWaitLimitNs the waiting thread records a
 // code in `status`, raises the CTA's abort flag and every role leaves its loop;
@@ -52,6 +54,8 @@ constexpr uint64_t kDrainNs = 20000000ull;        // 20 ms drain on the abort pa
 struct GemmParams {
   CUtensorMap a0, a1;      // A operand(s); a1 only in MODE_DX (second product)
   CUtensorMap b0, b1;      // B operands (gate, up)
+  // MODE_FWD store maps for g, u and out: boxes of 32 rows x 32 columns, 64-byte swizzle
+  CUtensorMap sg, su, so;
   uint64_t a_desc, b_desc; // UMMA shared-memory descriptors with a zero start address
   uint32_t a_kadv, b_kadv; // bytes to advance the start address per K=16 step
   uint32_t idesc;          // UMMA instruction descriptor
@@ -260,90 +264,132 @@ __device__ __forceinline__ void flush_rows128(uint32_t buf, int lane, void* out,
   }
 }
 
-// SwiGLU epilogue over one 256-column region laid out [128 gate | 128 up]:
-// 64-column boxes jb in [jb_begin, jb_end).  `release` is called right after
-// the last tensor-memory read.
-template <class C, typename T, bool ACC16, class Release>
-__device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& e, uint32_t taddr,
-                                             int n0, int jb_begin, int jb_end, Release release) {
-  const uint32_t buf0 = e.buf, buf1 = e.buf + 2048u;
-#pragma unroll 1
-  for (int jb = jb_begin; jb < jb_end; ++jb) {
-#pragma unroll 1
-    for (int h = 0; h < 2; ++h) {
-      uint32_t rg[32], ru[32];
-      ptx::tmem_ld_32x32(taddr + jb * 64 + h * 32, rg);
-      ptx::tmem_ld_32x32(taddr + 128 + jb * 64 + h * 32, ru);
-      ptx::tmem_ld_wait();
-      if (jb == jb_end - 1 && h == 1) release();
-      uint32_t pg[16], pu[16], po[16];
+// Unpack a packed pair of 16-bit values to fp32.
+template <typename T>
+__device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi);
+template <>
+__device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t w, float& lo, float& hi) {
+  lo = __uint_as_float(w << 16);
+  hi = __uint_as_float(w & 0xFFFF0000u);
+}
+template <>
+__device__ __forceinline__ void unpack2<__half>(uint32_t w, float& lo, float& hi) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+  lo = f.x;
+  hi = f.y;
+}
+
+// Product of two packed 16-bit pairs, each lane rounded once to the 16-bit type -
+// bit-identical to multiplying in fp32 (the product of two 16-bit values is exact
+// there) and rounding.
+template <typename T>
+__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b);
+template <>
+__device__ __forceinline__ uint32_t mul2<__nv_bfloat16>(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a),
+                                   *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <>
+__device__ __forceinline__ uint32_t mul2<__half>(uint32_t a, uint32_t b) {
+  const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// Read 16 accumulator columns and round them to 8 packed 16-bit pairs.
+template <typename T, bool ACC16>
+__device__ __forceinline__ void load_pack16(uint32_t taddr, uint32_t* dst8) {
+  uint32_t r[16];
+  ptx::tmem_ld_32x16(taddr, r);
+  ptx::tmem_ld_wait();
 #pragma unroll
-      for (int q = 0; q < 16; ++q) {
-        const int c0 = 2 * q;
-        if (ACC16) {
-          // fp16 accumulators sit in the low half of each 32-bit column.
-          const __half g0 = __ushort_as_half(static_cast<unsigned short>(rg[c0]));
-          const __half g1 = __ushort_as_half(static_cast<unsigned short>(rg[c0 + 1]));
-          const __half u0 = __ushort_as_half(static_cast<unsigned short>(ru[c0]));
-          const __half u1 = __ushort_as_half(static_cast<unsigned short>(ru[c0 + 1]));
-          const float gf0 = __half2float(g0), gf1 = __half2float(g1);
-          const __half s0 = __float2half_rn(gf0 * sigmoid_f32(gf0));
-          const __half s1 = __float2half_rn(gf1 * sigmoid_f32(gf1));
-          const __half2 o = __hmul2(__halves2half2(u0, u1), __halves2half2(s0, s1));
-          pg[q] = (rg[c0] & 0xFFFFu) | (rg[c0 + 1] << 16);
-          pu[q] = (ru[c0] & 0xFFFFu) | (ru[c0 + 1] << 16);
-          po[q] = *reinterpret_cast<const uint32_t*>(&o);
-        } else {
-          const float g0 = __uint_as_float(rg[c0]), g1 = __uint_as_float(rg[c0 + 1]);
-          const float u0 = __uint_as_float(ru[c0]), u1 = __uint_as_float(ru[c0 + 1]);
-          const float s0 = round16<T>(g0 * sigmoid_f32(g0));
-          const float s1 = round16<T>(g1 * sigmoid_f32(g1));
-          pg[q] = pack2<T>(g0, g1);
-          pu[q] = pack2<T>(u0, u1);
-          po[q] = pack2<T>(u0 * s0, u1 * s1);
-        }
-      }
-      const int col = n0 + jb * 64 + h * 32;
-      if (p.store_gu) {
-        stage_rows64(buf0, e.lane, pg);
-        stage_rows64(buf1, e.lane, pu);
-        __syncwarp();
-        flush_rows64(buf0, e.lane, p.c0_ptr, e.row0, col, p.M, p.N);
-        flush_rows64(buf1, e.lane, p.c1_ptr, e.row0, col, p.M, p.N);
-        __syncwarp();
-      }
-      stage_rows64(buf0, e.lane, po);
+  for (int q = 0; q < 8; ++q) {
+    if (ACC16)  // fp16 accumulators sit in the low half of each 32-bit column
+      dst8[q] = __byte_perm(r[2 * q], r[2 * q + 1], 0x5410);
+    else
+      dst8[q] = pack2<T>(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1]));
+  }
+}
+
+// SwiGLU epilogue over 64-column boxes jb in [jb_begin, jb_begin + NJB) of one
+// 256-column region laid out [128 gate | 128 up].
+//
+// Phase A reads the warp's accumulators, rounds them to the 16-bit g and u that are
+// stored anyway, keeps them packed in registers and calls `release`, so the MMA
+// issuer can refill the region while phase B runs.  Phase B computes
+// out = round(round(silu_f32(g16)) * u16) - the rounding order of the reference's
+// PyTorch oracle (test_swiglu.py:47-55), every op rounding to the tensor dtype -
+// and hands g, u and out to TMA stores as 32x32 boxes from the warp's two swizzled
+// 2 KB staging buffers.  A buffer is rewritten only after the bulk group that read it
+// has finished reading; phase B overlaps the next tile's MMAs, so these waits are
+// off the critical path.
+template <class C, typename T, bool ACC16, int NJB, class Release>
+__device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& e, uint32_t taddr,
+                                             int n0, int jb_begin, Release release) {
+  const uint32_t buf0 = e.buf, buf1 = e.buf + 2048u;
+  const bool rows_ok = e.row0 < p.M;
+  uint32_t G[NJB * 32], U[NJB * 32];
+#pragma unroll
+  for (int c = 0; c < NJB * 4; ++c) {
+    load_pack16<T, ACC16>(taddr + jb_begin * 64 + c * 16, &G[c * 8]);
+    load_pack16<T, ACC16>(taddr + 128 + jb_begin * 64 + c * 16, &U[c * 8]);
+  }
+  release();
+#pragma unroll
+  for (int c = 0; c < NJB * 2; ++c) {
+    const uint32_t* pg = &G[c * 16];
+    const uint32_t* pu = &U[c * 16];
+    const int col = n0 + jb_begin * 64 + c * 32;
+    const bool in_range = rows_ok && col < p.N;
+    if (p.store_gu) {
+      if (e.lane == 0) ptx::tma_store_wait_read<0>();
       __syncwarp();
-      flush_rows64(buf0, e.lane, p.c2_ptr, e.row0, col, p.M, p.N);
+      stage_rows64(buf0, e.lane, *reinterpret_cast<const uint32_t(*)[16]>(pg));
+      stage_rows64(buf1, e.lane, *reinterpret_cast<const uint32_t(*)[16]>(pu));
+      ptx::fence_proxy_async_smem();
       __syncwarp();
+      if (e.lane == 0 && in_range) {
+        ptx::tma_store_2d(&p.sg, buf0, col, e.row0);
+        ptx::tma_store_2d(&p.su, buf1, col, e.row0);
+        ptx::tma_store_commit();
+      }
+    }
+    uint32_t po[16];
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {
+      float g0, g1;
+      unpack2<T>(pg[q], g0, g1);
+      po[q] = mul2<T>(pack2<T>(g0 * sigmoid_f32(g0), g1 * sigmoid_f32(g1)), pu[q]);
+    }
+    if (e.lane == 0) ptx::tma_store_wait_read<0>();
+    __syncwarp();
+    stage_rows64(buf0, e.lane, po);
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (e.lane == 0 && in_range) {
+      ptx::tma_store_2d(&p.so, buf0, col, e.row0);
+      ptx::tma_store_commit();
     }
   }
 }
 
-// Plain epilogue over one 256-column region: 64-column boxes jb in
-// [jb_begin, jb_end).  MODE_DX: all four boxes belong to c0 at columns
-// n0 + 64*jb; MODE_DW: boxes 0,1 -> c0, boxes 2,3 -> c1, at n0 + 64*(jb&1).
-template <class C, int MODE, typename T, bool ACC16, class Release>
+// Plain epilogue over 64-column boxes jb in [jb_begin, jb_begin + NJB) of one
+// 256-column region.  MODE_DX: all four boxes belong to c0 at columns n0 + 64*jb;
+// MODE_DW: boxes 0,1 -> c0, boxes 2,3 -> c1, at n0 + 64*(jb&1).  Each box is read,
+// rounded, transposed through the staging buffer and written with row-coalesced
+// stores; `release` is called right after the last tensor-memory read.  (These
+// GEMMs have K loops of 400+ blocks per tile, so the few thousand cycles this
+// takes are ~1 % of a tile and are not worth the registers a two-phase drain needs.)
+template <class C, int MODE, typename T, bool ACC16, int NJB, class Release>
 __device__ __forceinline__ void drain_plain(const GemmParams& p, const EpiCtx& e, uint32_t taddr,
-                                            int n0, int jb_begin, int jb_end, Release release) {
+                                            int n0, int jb_begin, Release release) {
 #pragma unroll 1
-  for (int jb = jb_begin; jb < jb_end; ++jb) {
-    uint32_t r0[32], r1[32];
-    ptx::tmem_ld_32x32(taddr + jb * 64, r0);
-    ptx::tmem_ld_32x32(taddr + jb * 64 + 32, r1);
-    ptx::tmem_ld_wait();
-    if (jb == jb_end - 1) release();
+  for (int j = 0; j < NJB; ++j) {
+    const int jb = jb_begin + j;
     uint32_t pk[32];
 #pragma unroll
-    for (int q = 0; q < 16; ++q) {
-      if (ACC16) {
-        pk[q] = (r0[2 * q] & 0xFFFFu) | (r0[2 * q + 1] << 16);
-        pk[16 + q] = (r1[2 * q] & 0xFFFFu) | (r1[2 * q + 1] << 16);
-      } else {
-        pk[q] = pack2<T>(__uint_as_float(r0[2 * q]), __uint_as_float(r0[2 * q + 1]));
-        pk[16 + q] = pack2<T>(__uint_as_float(r1[2 * q]), __uint_as_float(r1[2 * q + 1]));
-      }
-    }
+    for (int c = 0; c < 4; ++c) load_pack16<T, ACC16>(taddr + jb * 64 + c * 16, &pk[c * 8]);
+    if (j == NJB - 1) release();
     const int col = (MODE == MODE_DX) ? (n0 + jb * 64) : (n0 + (jb & 1) * 64);
     void* out = (MODE == MODE_DW && jb >= 2) ? p.c1_ptr : p.c0_ptr;
     stage_rows128(e.buf, e.lane, pk);
@@ -404,6 +450,11 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
     ptx::prefetch_tensormap(&p.b0);
     ptx::prefetch_tensormap(&p.b1);
     if (MODE == MODE_DX) ptx::prefetch_tensormap(&p.a1);
+    if (MODE == MODE_FWD) {
+      ptx::prefetch_tensormap(&p.sg);
+      ptx::prefetch_tensormap(&p.su);
+      ptx::prefetch_tensormap(&p.so);
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc<CG>(bar_base + 8u * (2 * STAGES + 4), C::TMEM_COLS);
@@ -617,13 +668,15 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
         if (FSW_DBG_SKIP_EPILOGUE) {
           release();
         } else if (MODE == MODE_FWD) {
-          const int jb0 = split ? chalf : 0;
-          const int jb1 = split ? chalf + 1 : 2;
-          drain_swiglu<C, T, ACC16>(p, e, taddr, rn0, jb0, jb1, release);
+          if (split)
+            drain_swiglu<C, T, ACC16, 1>(p, e, taddr, rn0, chalf, release);
+          else
+            drain_swiglu<C, T, ACC16, 2>(p, e, taddr, rn0, 0, release);
         } else {
-          const int jb0 = split ? 2 * chalf : 0;
-          const int jb1 = split ? 2 * chalf + 2 : 4;
-          drain_plain<C, MODE, T, ACC16>(p, e, taddr, rn0, jb0, jb1, release);
+          if (split)
+            drain_plain<C, MODE, T, ACC16, 2>(p, e, taddr, rn0, 2 * chalf, release);
+          else
+            drain_plain<C, MODE, T, ACC16, 4>(p, e, taddr, rn0, 0, release);
         }
       }
       if (FSW_PROFILE) prof_drain += clock64() - prof_t0;
@@ -633,6 +686,11 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
         a ^= 1;
         if (a == 0) aph ^= 1u;
       }
+    }
+    if (MODE == MODE_FWD) {
+      // all bulk stores of this warp must have completed before the CTA exits
+      if (lane == 0) ptx::tma_store_wait_all<0>();
+      __syncwarp();
     }
     if (FSW_PROFILE && blockIdx.x == 0 && warp == 2 && lane == 0 && p.clk_probe != nullptr) {
       p.clk_probe[4] = prof_wait;

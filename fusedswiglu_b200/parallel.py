@@ -16,13 +16,19 @@ standard tensor-parallel MLP split and keeps the single-GPU numerics per shard.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
 import torch.distributed as dist
 from torch.autograd import Function
 
-from . import _launch
+from . import _launch, _lib
+
+# SMs left free for the all-reduce kernel while the dW GEMM runs.  The GEMMs are
+# persistent and would otherwise occupy every SM, so that NCCL's kernel could not
+# start before they finish and the collective would not overlap anything.
+COMM_SMS = int(os.environ.get("FSW_COMM_SMS", "16"))
 
 
 def shard_bounds(d_intermediate: int, rank: int, world_size: int) -> Tuple[int, int]:
@@ -61,6 +67,18 @@ class _CudaBackend:
     grad_input = staticmethod(_launch.grad_input)
     grad_weights = staticmethod(_launch.grad_weights)
 
+    @staticmethod
+    def grad_weights_beside_collective(x2d, dg, du, *, fast_accum=False):
+        """dW GEMM on all but COMM_SMS SMs, so a concurrent collective can run."""
+        if COMM_SMS <= 0:
+            return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum)
+        sms = _lib.get_option("sm_count")
+        _lib.set_option("gemm_max_sms", max(2, sms - COMM_SMS))
+        try:
+            return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum)
+        finally:
+            _lib.set_option("gemm_max_sms", 0)
+
 
 class ColumnParallelSwiGLU(Function):
     """``ColumnParallelSwiGLU.apply(x, w_gate_shard, w_up_shard, group=None)``.
@@ -94,7 +112,10 @@ class ColumnParallelSwiGLU(Function):
         work = None
         if dist.is_initialized() and dist.get_world_size(group) > 1:
             work = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group, async_op=True)
-        dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=fast_accum)
+        if work is not None and hasattr(backend, "grad_weights_beside_collective"):
+            dwg, dwu = backend.grad_weights_beside_collective(x2d, dg, du, fast_accum=fast_accum)
+        else:
+            dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=fast_accum)
         if work is not None:
             work.wait()
         return dx.view(bs, sq, dm), dwg, dwu, None, None, None

@@ -133,6 +133,13 @@ def swiglu_ref(x: np.ndarray, w_gate: np.ndarray, w_up: np.ndarray, dtype: str =
     return out.reshape(*x.shape[:-1], w_gate.shape[1])
 
 
+def swiglu_from_saved(g: np.ndarray, u: np.ndarray, dtype: str = "bf16") -> np.ndarray:
+    """out from the 16-bit g = x@w_gate and u = x@w_up, with the rounding points of
+    ``silu(x_gate) * x_up`` on 16-bit tensors (test_swiglu.py:52-55): silu evaluated
+    in fp32 and rounded, then the product rounded."""
+    return round16(round16(silu_f32(g), dtype) * u, dtype)
+
+
 def swiglu_ref_backward(
     x: np.ndarray, w_gate: np.ndarray, w_up: np.ndarray, dy: np.ndarray, dtype: str = "bf16"
 ) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
