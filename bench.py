@@ -43,7 +43,13 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 
 # DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum)
 # for the kernel named, on the workload named; see profiles/.  None = not captured.
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    # profiles/dram_traffic_llama3_8b_mlp.md (one launch each, full-size workload)
+    ("fwd_dual_gemm", "llama3_8b_mlp", 1): 5.12e9 + 2.79e9,
+    ("dx_gemm", "llama3_8b_mlp", 1): 8.90e9 + 0.26e9,
+    ("dw_dual_gemm", "llama3_8b_mlp", 1): 8.71e9 + 0.24e9,
+    ("gate_grad_elementwise", "llama3_8b_mlp", 1): 2.82e9 + 1.82e9,
+}
 
 CLOCK_QUERY = (
     "timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -62,6 +68,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
+                    help="library tuning knob passed to fsw_set_option, e.g. --opt group_m=16 (repeatable)")
     ap.add_argument("--only", default=None, choices=["fwd", "ew", "dx", "dw"],
                     help="launch only this kernel in each step (for profiling one kernel); prints no bench line")
     return ap.parse_args()
@@ -227,6 +235,9 @@ def run_ours(args):
     from fusedswiglu_b200 import FusedSwiGLU, _launch, _lib, parallel
 
     _lib.load()
+    for item in args.opt:
+        name, _, value = item.partition("=")
+        _lib.set_option(name, int(value))
     bs, sq, dm, di, dtype = WORKLOADS[args.workload]
     tdt = {"bf16": torch.bfloat16, "fp16": torch.float16}[dtype]
     T = bs * sq
@@ -419,6 +430,11 @@ def run_ours(args):
         "frac_of_nominal": kern[dom]["achieved"] / NOMINAL_BF16_TFLOPS,
         "algorithmic_flops_per_launch": gemm_flops_local,
         "traffic": NCU_TRAFFIC_BYTES.get((dom, args.workload, world)),
+        "algorithmic_hbm_bytes_per_launch": {
+            "fwd_dual_gemm": 2.0 * (T * dm + 2 * dm * di_local + 3 * T * di_local),
+            "dx_gemm": 2.0 * (2 * T * di_local + 2 * dm * di_local + T * dm),
+            "dw_dual_gemm": 2.0 * (T * dm + 2 * T * di_local + 2 * dm * di_local),
+        }[dom],
         "kernels": kern,
     }
     fwd_tokens_per_s = T / (per_kernel_ms[0] / 1e3)

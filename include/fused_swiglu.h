@@ -139,9 +139,13 @@ int fsw_query_device(int device, int* sm_count, int* cc_major, int* cc_minor,
 int64_t fsw_status(void);
 
 /*
- * Tuning and debugging knobs, process-wide.  Known names: "cta_group" (1 or 2),
- * "group_m" (tile-rasterisation group height, in tiles).  Returns FSW_EINVAL for
- * an unknown name or value.  fsw_get_option returns the current value or -1.
+ * Tuning and debugging knobs, process-wide.  Main names: "cta_group" (1 or 2 CTAs
+ * per MMA), "nsub" (1 or 2 accumulator regions per tile), "group_m" (tile
+ * rasterisation group height in tiles, 0 = automatic), "gemm_max_sms" (cap on the
+ * SMs a GEMM launch occupies, 0 = all; used to leave room for a concurrent
+ * collective), "ew_blocks_per_sm".  Read-only facts through fsw_get_option:
+ * "sm_count", "max_pairs", "stages", "last_sm_khz".  Returns FSW_EINVAL for an
+ * unknown name or value.  fsw_get_option returns the current value or -1.
  */
 int fsw_set_option(const char* name, int64_t value);
 int64_t fsw_get_option(const char* name);
