@@ -192,6 +192,29 @@ def test_reference_backward_suite():
     assert max(worst.values()) < EXPECTED_BF16
 
 
+@pytest.mark.parametrize("opts", [
+    {"cta_group": 1, "nsub": 1}, {"cta_group": 2, "nsub": 1}, {"cta_group": 2, "nsub": 2},
+    {"gemm_max_sms": 100}, {"gemm_max_sms": 3}, {"group_m": 1}, {"group_m": 5}, {"l2_a": 2},
+])
+def test_tile_and_scheduling_options_do_not_change_results(opts):
+    """Every tile shape / rasterisation / SM-cap setting computes the same GEMMs, so
+    the results must be bit-identical to the default configuration."""
+    from fusedswiglu_b200 import _lib
+
+    inp = orc.make_inputs(1, 1344, 448, 1216, "bf16", seed=21, dout_std=0.5)
+    base = run_cuda(inp, "bf16")
+    old = {k: _lib.get_option(k) for k in opts}
+    try:
+        for k, v in opts.items():
+            _lib.set_option(k, v)
+        got = run_cuda(inp, "bf16")
+    finally:
+        for k, v in old.items():
+            _lib.set_option(k, v)
+    for k in base:
+        assert np.array_equal(got[k], base[k]), (opts, k)
+
+
 # ------------------------------------------------------------- fp16 paths --
 @pytest.mark.parametrize("d_model", [1024, 2048])
 def test_fp16_fast_accum_against_fp32_accum(d_model):
