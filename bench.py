@@ -271,7 +271,7 @@ def run_ours(args):
         if marks: marks[3].record()
         if world > 1:
             work = dist.all_reduce(dx, async_op=True)
-            dwg, dwu = parallel._CudaBackend.grad_weights_beside_collective(x2d, dg, du)
+            dwg, dwu = parallel._CudaBackend.grad_weights_beside_collective(x2d, dg, du, world_size=world)
         else:
             work = None
             dwg, dwu = _launch.grad_weights(x2d, dg, du)
@@ -488,7 +488,7 @@ def run_ours(args):
         "config": {"workload": args.workload, "bs": bs, "sq": sq, "d_model": dm, "d_intermediate": di,
                    "parallelism": f"column-parallel d_intermediate x{world}" if world > 1 else "single GPU",
                    "l2": "inputs larger than L2 (activations and weights exceed 126 MB); no flush",
-                   "comm_sms_reserved_during_dw": parallel.COMM_SMS if world > 1 else 0,
+                   "comm_sms_reserved_during_dw": parallel.comm_sms(world) if world > 1 else 0,
                    "accumulate": "fp32", "cta_group": _lib.get_option("cta_group"),
                    "group_m": _lib.get_option("group_m")},
         "frac_of_nominal_bf16_peak": value / (NOMINAL_BF16_TFLOPS * world),

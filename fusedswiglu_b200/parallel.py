@@ -27,8 +27,18 @@ from . import _launch, _lib
 
 # SMs left free for the all-reduce kernel while the dW GEMM runs.  The GEMMs are
 # persistent and would otherwise occupy every SM, so that NCCL's kernel could not
-# start before they finish and the collective would not overlap anything.
-COMM_SMS = int(os.environ.get("FSW_COMM_SMS", "16"))
+# start before they finish and the collective would not overlap anything.  NCCL's
+# all-reduce only makes progress once all of its CTAs are resident: measured on
+# 8xB200, 2 ranks overlap fully with 16 free SMs (exposed 0.33 -> 0.003 ms), 4 and
+# 8 ranks (32 channels) need 32 (8 ranks: exposed 0.60 -> 0.18 ms; 24 or 28 free SMs
+# change nothing).  FSW_COMM_SMS overrides; 0 disables the cap.
+_COMM_SMS_ENV = os.environ.get("FSW_COMM_SMS")
+
+
+def comm_sms(world_size: int) -> int:
+    if _COMM_SMS_ENV is not None:
+        return int(_COMM_SMS_ENV)
+    return 16 if world_size <= 2 else 32
 
 
 def shard_bounds(d_intermediate: int, rank: int, world_size: int) -> Tuple[int, int]:
@@ -68,12 +78,13 @@ class _CudaBackend:
     grad_weights = staticmethod(_launch.grad_weights)
 
     @staticmethod
-    def grad_weights_beside_collective(x2d, dg, du, *, fast_accum=False):
-        """dW GEMM on all but COMM_SMS SMs, so a concurrent collective can run."""
-        if COMM_SMS <= 0:
+    def grad_weights_beside_collective(x2d, dg, du, *, fast_accum=False, world_size=2):
+        """dW GEMM on all but comm_sms(world_size) SMs, so a concurrent collective can run."""
+        reserve = comm_sms(world_size)
+        if reserve <= 0:
             return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum)
         sms = _lib.get_option("sm_count")
-        _lib.set_option("gemm_max_sms", max(2, sms - COMM_SMS))
+        _lib.set_option("gemm_max_sms", max(2, sms - reserve))
         try:
             return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum)
         finally:
@@ -113,7 +124,8 @@ class ColumnParallelSwiGLU(Function):
         if dist.is_initialized() and dist.get_world_size(group) > 1:
             work = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group, async_op=True)
         if work is not None and hasattr(backend, "grad_weights_beside_collective"):
-            dwg, dwu = backend.grad_weights_beside_collective(x2d, dg, du, fast_accum=fast_accum)
+            dwg, dwu = backend.grad_weights_beside_collective(
+                x2d, dg, du, fast_accum=fast_accum, world_size=dist.get_world_size(group))
         else:
             dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=fast_accum)
         if work is not None:
