@@ -36,6 +36,11 @@ WORKLOADS = {
     "readme": (4, 2048, 4096, 12288, "bf16"),
     "llama3_70b_mlp": (16, 4096, 8192, 28672, "bf16"),
     "plumbing": (1, 128, 512, 1536, "bf16"),
+    # fp16 sweep with the fp16 tensor-memory accumulator (FastAccumFusedSwiGLU): d_intermediate = 3*d_model
+    "fp16_d1024": (4, 2048, 1024, 3072, "fp16"),
+    "fp16_d2048": (4, 2048, 2048, 6144, "fp16"),
+    "fp16_d4096": (4, 2048, 4096, 12288, "fp16"),
+    "fp16_d8192": (4, 2048, 8192, 24576, "fp16"),
 }
 DEFAULT_WORKLOAD = "llama3_8b_mlp"
 NOMINAL_BF16_TFLOPS = 2250.0
@@ -68,6 +73,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--fp32-accum", action="store_true",
+                    help="fp16 workloads: accumulate in fp32 instead of the fp16 accumulator")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="library tuning knob passed to fsw_set_option, e.g. --opt group_m=16 (repeatable)")
     ap.add_argument("--only", default=None, choices=["fwd", "ew", "dx", "dw"],
@@ -232,7 +239,7 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    from fusedswiglu_b200 import FusedSwiGLU, _launch, _lib, parallel
+    from fusedswiglu_b200 import FastAccumFusedSwiGLU, FusedSwiGLU, _launch, _lib, parallel
 
     _lib.load()
     for item in args.opt:
@@ -240,6 +247,8 @@ def run_ours(args):
         _lib.set_option(name, int(value))
     bs, sq, dm, di, dtype = WORKLOADS[args.workload]
     tdt = {"bf16": torch.bfloat16, "fp16": torch.float16}[dtype]
+    fast = dtype == "fp16" and not args.fp32_accum  # fp16 accumulator in forward and dW
+    FastAccumFusedSwiGLU.fast_accum = fast
     T = bs * sq
     lo, hi = parallel.shard_bounds(di, rank, world)
     di_local = hi - lo
@@ -255,6 +264,8 @@ def run_ours(args):
     wu = wu_full[:, lo:hi].contiguous()
     del wg_full, wu_full
     dout = torch.randn(bs, sq, di_local, device=dev, dtype=tdt, generator=g)
+    if dtype == "fp16":
+        dout *= 0.1  # the reference's dy = 0.1 * randn (test_swiglu.py:98)
     x2d = x.view(T, dm)
     dout2d = dout.view(T, di_local)
 
@@ -263,7 +274,7 @@ def run_ours(args):
 
     def step(marks=None):
         if marks: marks[0].record()
-        out, gg, uu = _launch.forward(x2d, wg, wu)
+        out, gg, uu = _launch.forward(x2d, wg, wu, fast_accum=fast)
         if marks: marks[1].record()
         dg, du = _launch.gate_grad(dout2d, gg, uu)
         if marks: marks[2].record()
@@ -271,10 +282,11 @@ def run_ours(args):
         if marks: marks[3].record()
         if world > 1:
             work = dist.all_reduce(dx, async_op=True)
-            dwg, dwu = parallel._CudaBackend.grad_weights_beside_collective(x2d, dg, du, world_size=world)
+            dwg, dwu = parallel._CudaBackend.grad_weights_beside_collective(
+                x2d, dg, du, fast_accum=fast, world_size=world)
         else:
             work = None
-            dwg, dwu = _launch.grad_weights(x2d, dg, du)
+            dwg, dwu = _launch.grad_weights(x2d, dg, du, fast_accum=fast)
         if marks: marks[4].record()
         if work is not None:
             work.wait()
@@ -287,13 +299,13 @@ def run_ours(args):
 
     if args.only:
         # Profiling aid: the other kernels run once to produce this kernel's inputs.
-        out, gg, uu = _launch.forward(x2d, wg, wu)
+        out, gg, uu = _launch.forward(x2d, wg, wu, fast_accum=fast)
         dg, du = _launch.gate_grad(dout2d, gg, uu)
         one = {
-            "fwd": lambda: _launch.forward(x2d, wg, wu),
+            "fwd": lambda: _launch.forward(x2d, wg, wu, fast_accum=fast),
             "ew": lambda: _launch.gate_grad(dout2d, gg, uu),
             "dx": lambda: _launch.grad_input(dg, du, wg, wu),
-            "dw": lambda: _launch.grad_weights(x2d, dg, du),
+            "dw": lambda: _launch.grad_weights(x2d, dg, du, fast_accum=fast),
         }[args.only]
         for _ in range(W):
             one()
@@ -389,7 +401,9 @@ def run_ours(args):
             xin = x_dev[b].detach().requires_grad_(True)
             wgp.grad = wup.grad = None
             if world > 1:
-                out = parallel.column_parallel_swiglu(xin, wgp, wup)
+                out = parallel.column_parallel_swiglu(xin, wgp, wup, fast_accum=fast)
+            elif dtype == "fp16":
+                out = FastAccumFusedSwiGLU.apply(xin, wgp, wup)
             else:
                 out = FusedSwiGLU.apply(xin, wgp, wup)
             out.backward(dout_dev[b])
@@ -430,7 +444,8 @@ def run_ours(args):
         e2e = {"value": total_flops / e2e_ms / 1e9, "unit": "TFLOP/s",
                "h2d_bytes_per_step": hx.numel() * 2 + hdout.numel() * 2, "d2h_bytes_per_step": hdx.numel() * 2,
                "ms_per_step": e2e_ms, "steps": n_e2e,
-               "api": "FusedSwiGLU.apply + backward" if world == 1 else "ColumnParallelSwiGLU.apply + backward",
+               "api": ("FastAccumFusedSwiGLU" if dtype == "fp16" else "FusedSwiGLU") + ".apply + backward"
+               if world == 1 else "ColumnParallelSwiGLU.apply + backward",
                "note": "every step uploads its x and dout from pinned host memory and downloads its dX; "
                        "uploads for step i+1 and the download of step i overlap step i's kernels "
                        "(double-buffered); weights stay resident"}
@@ -489,7 +504,7 @@ def run_ours(args):
                    "parallelism": f"column-parallel d_intermediate x{world}" if world > 1 else "single GPU",
                    "l2": "inputs larger than L2 (activations and weights exceed 126 MB); no flush",
                    "comm_sms_reserved_during_dw": parallel.comm_sms(world) if world > 1 else 0,
-                   "accumulate": "fp32", "cta_group": _lib.get_option("cta_group"),
+                   "accumulate": "fp16 accumulator in forward and dW, fp32 in dX" if fast else "fp32", "cta_group": _lib.get_option("cta_group"),
                    "group_m": _lib.get_option("group_m")},
         "frac_of_nominal_bf16_peak": value / (NOMINAL_BF16_TFLOPS * world),
         "frac_of_measured_sustained": value / (peaks["bf16_tflops_sustained"] * world),

@@ -311,6 +311,26 @@ __device__ __forceinline__ void load_pack16(uint32_t taddr, uint32_t* dst8) {
   }
 }
 
+// Read 16 gate and 16 up columns with both loads in flight, rounded to 8 + 8 pairs.
+template <typename T, bool ACC16>
+__device__ __forceinline__ void load_pack16x2(uint32_t taddr_g, uint32_t taddr_u, uint32_t* g8,
+                                              uint32_t* u8) {
+  uint32_t rg[16], ru[16];
+  ptx::tmem_ld_32x16(taddr_g, rg);
+  ptx::tmem_ld_32x16(taddr_u, ru);
+  ptx::tmem_ld_wait();
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    if (ACC16) {
+      g8[q] = __byte_perm(rg[2 * q], rg[2 * q + 1], 0x5410);
+      u8[q] = __byte_perm(ru[2 * q], ru[2 * q + 1], 0x5410);
+    } else {
+      g8[q] = pack2<T>(__uint_as_float(rg[2 * q]), __uint_as_float(rg[2 * q + 1]));
+      u8[q] = pack2<T>(__uint_as_float(ru[2 * q]), __uint_as_float(ru[2 * q + 1]));
+    }
+  }
+}
+
 // SwiGLU epilogue over 64-column boxes jb in [jb_begin, jb_begin + NJB) of one
 // 256-column region laid out [128 gate | 128 up].
 //
@@ -330,10 +350,9 @@ __device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& 
   const bool rows_ok = e.row0 < p.M;
   uint32_t G[NJB * 32], U[NJB * 32];
 #pragma unroll
-  for (int c = 0; c < NJB * 4; ++c) {
-    load_pack16<T, ACC16>(taddr + jb_begin * 64 + c * 16, &G[c * 8]);
-    load_pack16<T, ACC16>(taddr + 128 + jb_begin * 64 + c * 16, &U[c * 8]);
-  }
+  for (int c = 0; c < NJB * 4; ++c)
+    load_pack16x2<T, ACC16>(taddr + jb_begin * 64 + c * 16, taddr + 128 + jb_begin * 64 + c * 16,
+                            &G[c * 8], &U[c * 8]);
   release();
 #pragma unroll
   for (int c = 0; c < NJB * 2; ++c) {

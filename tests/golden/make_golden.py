@@ -38,7 +38,9 @@ def sha(a: np.ndarray) -> str:
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/fusedswiglu")
+    ref_root = sys.argv[1]
     sys.path.insert(0, str(REPO))
     from oracle import swiglu_oracle as orc
 
