@@ -504,8 +504,8 @@ def run_ours(args):
                    "parallelism": f"column-parallel d_intermediate x{world}" if world > 1 else "single GPU",
                    "l2": "inputs larger than L2 (activations and weights exceed 126 MB); no flush",
                    "comm_sms_reserved_during_dw": parallel.comm_sms(world) if world > 1 else 0,
-                   "accumulate": "fp16 accumulator in forward and dW, fp32 in dX" if fast else "fp32", "cta_group": _lib.get_option("cta_group"),
-                   "group_m": _lib.get_option("group_m")},
+                   "accumulate": "fp16 accumulator in forward and dW, fp32 in dX" if fast else "fp32", "tile_options": {k: _lib.get_option(k) for k in ("cta_group", "nsub", "group_m")},
+                   "tile_note": "0 = chosen per launch; this workload gets CTA pairs, 256x512 tiles"},
         "frac_of_nominal_bf16_peak": value / (NOMINAL_BF16_TFLOPS * world),
         "frac_of_measured_sustained": value / (peaks["bf16_tflops_sustained"] * world),
         "fwd_tokens_per_s": fwd_tokens_per_s,

@@ -140,7 +140,8 @@ int64_t fsw_status(void);
 
 /*
  * Tuning and debugging knobs, process-wide.  Main names: "cta_group" (1 or 2 CTAs
- * per MMA), "nsub" (1 or 2 accumulator regions per tile), "group_m" (tile
+ * per MMA, 0 = automatic), "nsub" (1 or 2 accumulator regions per tile, 0 =
+ * automatic), "group_m" (tile
  * rasterisation group height in tiles, 0 = automatic), "gemm_max_sms" (cap on the
  * SMs a GEMM launch occupies, 0 = all; used to leave room for a concurrent
  * collective), "ew_blocks_per_sm".  Read-only facts through fsw_get_option:

@@ -68,11 +68,12 @@ def test_against_reference_golden(name, cta_group):
     from fusedswiglu_b200 import _lib
 
     c = load_golden(name)
+    old = _lib.get_option("cta_group")
     _lib.set_option("cta_group", cta_group)
     try:
         got = run_cuda(c, c["dtype"])
     finally:
-        _lib.set_option("cta_group", 2)
+        _lib.set_option("cta_group", old)
     step = c["row_step"]
     got["dw_gate"], got["dw_up"] = got["dw_gate"][::step], got["dw_up"][::step]
     expected = EXPECTED_BF16 if c["dtype"] == "bf16" else EXPECTED_FP16
