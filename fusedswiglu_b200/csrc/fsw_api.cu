@@ -39,6 +39,8 @@ struct Options {
   int64_t cta_group = 0;  // CTAs per MMA: 1, 2, or 0 = choose per launch
   int64_t nsub = 0;       // accumulator regions per tile: 1, 2 (needs a CTA pair), or 0 = choose
   int64_t group_m = 0;           // rasterisation group height in tiles; 0 = choose per launch
+  int64_t wait_limit_ms = 2000;  // bound on every device-side wait
+  int64_t stall_producer = 0;    // test hook: make the consumers' waits run out
   int64_t gemm_max_sms = 0;      // cap on SMs a GEMM launch occupies (0 = all of them)
   int64_t l2_a = 0, l2_b = 0;    // L2 eviction priority of A / B operand loads (0/1/2)
   int64_t ew_blocks_per_sm = 32;  // grid cap of the elementwise kernel, per SM
@@ -316,6 +318,8 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   p.clk_probe = d->clk_probe;
   p.l2_a = (int)g_opt.l2_a;
   p.l2_b = (int)g_opt.l2_b;
+  p.wait_limit_ns = (unsigned long long)g_opt.wait_limit_ms * 1000000ull;
+  p.stall_producer = (int)g_opt.stall_producer;
   const int a_major = (MODE == MODE_DW) ? MAJOR_MN : MAJOR_K;
   const int b_major = (MODE == MODE_DX) ? MAJOR_K : MAJOR_MN;
   fill_operand_desc(a_major, &p.a_desc, &p.a_kadv);
@@ -521,6 +525,12 @@ int fsw_set_option(const char* name, int64_t value) {
   } else if (!strcmp(name, "group_m")) {
     if (value < 0 || value > (1 << 20)) return fail(FSW_EINVAL, "group_m must be >= 0 (0 = automatic)");
     g_opt.group_m = value;
+  } else if (!strcmp(name, "wait_limit_ms")) {
+    if (value < 1 || value > 60000) return fail(FSW_EINVAL, "wait_limit_ms must be in [1, 60000]");
+    g_opt.wait_limit_ms = value;
+  } else if (!strcmp(name, "stall_producer")) {
+    if (value != 0 && value != 1) return fail(FSW_EINVAL, "stall_producer must be 0 or 1");
+    g_opt.stall_producer = value;
   } else if (!strcmp(name, "gemm_max_sms")) {
     if (value < 0) return fail(FSW_EINVAL, "gemm_max_sms must be >= 0");
     g_opt.gemm_max_sms = value;
@@ -555,6 +565,8 @@ int64_t fsw_get_option(const char* name) {
   if (!strcmp(name, "nsub")) return g_opt.nsub;
   if (!strcmp(name, "ew_blocks_per_sm")) return g_opt.ew_blocks_per_sm;
   if (!strcmp(name, "gemm_max_sms")) return g_opt.gemm_max_sms;
+  if (!strcmp(name, "wait_limit_ms")) return g_opt.wait_limit_ms;
+  if (!strcmp(name, "stall_producer")) return g_opt.stall_producer;
   if (!strcmp(name, "l2_a")) return g_opt.l2_a;
   if (!strcmp(name, "l2_b")) return g_opt.l2_b;
   if (!strcmp(name, "k_lbo")) return g_opt.k_lbo;

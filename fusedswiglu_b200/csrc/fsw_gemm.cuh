@@ -48,7 +48,7 @@ enum : uint32_t {
   WAIT_EPI_TMEM_FULL = 4,
 };
 
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s per wait
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // default limit per wait: 2 s
 constexpr uint64_t kDrainNs = 20000000ull;        // 20 ms drain on the abort path
 
 struct GemmParams {
@@ -67,6 +67,9 @@ struct GemmParams {
   uint32_t* status;        // device status word (0 = ok)
   void *c0_ptr, *c1_ptr, *c2_ptr;  // outputs (see the mode table above); row stride N
   unsigned long long* clk_probe;   // [2]: SM cycles and nanoseconds CTA 0 was resident
+  unsigned long long wait_limit_ns;  // every mbarrier wait gives up after this long
+  int stall_producer;              // test hook: the TMA producer issues nothing, so the
+                                   // consumers' bounded waits run out and the error path runs
 };
 
 // Epilogue warps: 4 (one per TMEM lane quadrant) or 8 (two per quadrant).
@@ -166,6 +169,7 @@ __device__ __forceinline__ float sigmoid_f32(float x) {
 struct AbortCtl {
   volatile uint32_t* flag;  // shared-memory abort flag of this CTA
   uint32_t* status;         // global status word
+  uint64_t limit_ns;        // how long one wait may last
 };
 
 // Wait by ONE thread.
@@ -178,7 +182,7 @@ __device__ __forceinline__ bool bounded_wait_thread(uint32_t bar, uint32_t parit
     if (ptx::mbar_try_wait(bar, parity)) return true;
     if ((++spins & 255u) == 0u) {
       if (*ctl.flag != 0u) return false;
-      if (ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (ptx::globaltimer_ns() - t0 > ctl.limit_ns) {
         *ctl.flag = code;
         atomicCAS(ctl.status, 0u, code | (static_cast<uint32_t>(blockIdx.x) << 8));
         return false;
@@ -439,7 +443,7 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
   const uint32_t misc_off = (bar_base - smem_base) + 8u * (2 * STAGES + 4);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + misc_off);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + misc_off + 4);
-  const AbortCtl ctl{abort_flag, p.status};
+  const AbortCtl ctl{abort_flag, p.status, p.wait_limit_ns ? p.wait_limit_ns : kWaitLimitNs};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -495,7 +499,7 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
 
   if (warp == 0) {
     // ======================= TMA producer (one thread) =======================
-    if (lane == 0 && !FSW_DBG_SKIP_LOADS) {
+    if (lane == 0 && !FSW_DBG_SKIP_LOADS && !p.stall_producer) {
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;

@@ -70,3 +70,11 @@ def test_options_roundtrip():
     with pytest.raises(_lib.FusedSwiGLUError):
         _lib.set_option("no_such_option", 1)
     assert _lib.get_option("no_such_option") == -1
+    # bounds of the device-wait limit and of the automatic settings
+    assert _lib.get_option("wait_limit_ms") == 2000
+    with pytest.raises(_lib.FusedSwiGLUError):
+        _lib.set_option("wait_limit_ms", 0)
+    for name in ("cta_group", "nsub", "group_m"):
+        assert _lib.get_option(name) == 0  # 0 = chosen per launch
+    with pytest.raises(_lib.FusedSwiGLUError):
+        _lib.set_option("nsub", 3)

@@ -479,3 +479,33 @@ def test_full_size_properties(T, dm, di):
     # permutation equivariance: reversing the tokens reverses the output rows
     outp, _, _ = _launch.forward(x.flip(0).contiguous(), wg, wu, save_activations=False)
     assert torch.equal(outp.flip(0), out)
+
+
+# ------------------------------------------------- bounded waits, error path --
+def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable():
+    """The TMA producer is told to issue nothing (a host-set test hook), so no
+    barrier is ever signalled: the consumers' bounded waits run out after the
+    (shortened) limit, the kernel records a status code, frees its tensor memory and
+    returns.  Nothing faults or hangs; the next launch works normally."""
+    from fusedswiglu_b200 import _launch, _lib
+
+    inp = orc.make_inputs(1, 256, 128, 256, "bf16", seed=4)
+    x, wg, wu = dev(inp["x"][0], "bf16"), dev(inp["w_gate"], "bf16"), dev(inp["w_up"], "bf16")
+    assert _lib.device_status() == 0
+    old_limit = _lib.get_option("wait_limit_ms")
+    _lib.set_option("wait_limit_ms", 100)
+    _lib.set_option("stall_producer", 1)
+    try:
+        _launch.forward(x, wg, wu)
+        torch.cuda.synchronize()  # returns: the kernel gave up by itself
+        with pytest.raises(_lib.FusedSwiGLUError) as err:
+            _lib.check("fsw_status", -4 if _lib.load().fsw_status() != 0 else 0)
+        assert "bounded wait" in str(err.value)
+    finally:
+        _lib.set_option("stall_producer", 0)
+        _lib.set_option("wait_limit_ms", old_limit)
+    assert _lib.device_status() == 0  # reading the status cleared it
+    out, g, u = _launch.forward(x, wg, wu)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert orc.rel_error(host(out), orc.swiglu_ref(inp["x"], inp["w_gate"], inp["w_up"], "bf16")[0]) < 1e-3
