@@ -12,7 +12,9 @@ Differences, all on the accurate side of the reference's tolerances:
     reference rounds per batch and sums in 16 bits, swiglu.py:51-57), and is
     returned as (d_model, d_intermediate) - autograd reduces the reference's
     (1, d_model, d_intermediate) to that shape anyway;
-  * gradients that autograd does not need are not computed.
+  * gradients that autograd does not need are not computed;
+  * with ``recompute`` the saved x@w_gate and x@w_up are dropped and recomputed in
+    backward (an activation-memory mode the reference does not have).
 """
 from __future__ import annotations
 
@@ -21,7 +23,7 @@ import torch
 from . import _launch
 
 
-def swiglu_forward(ctx, x, w_gate, w_up, *, fast_accum: bool):
+def swiglu_forward(ctx, x, w_gate, w_up, *, fast_accum: bool, recompute: bool = False):
     assert (
         x.shape[2] == w_up.shape[0]
     ), f"Dimension mismatch. Expected a.shape[2] ({x.shape[2]}) to be equal to b.shape[0] ({w_up.shape[0]})"
@@ -36,15 +38,24 @@ def swiglu_forward(ctx, x, w_gate, w_up, *, fast_accum: bool):
     # Grad mode is always off inside Function.forward; what autograd will ask for
     # is in ctx.needs_input_grad (all False under torch.no_grad()).
     need_grad = any(ctx.needs_input_grad[:3])
-    out, g, u = _launch.forward(x2d, wg, wu, fast_accum=fast_accum, save_activations=need_grad)
-    if need_grad:
+    # recompute: keep only x and the weights; backward runs the forward kernel again to
+    # get g and u (bit-identical), trading one extra dual GEMM for 2*T*di saved elements.
+    save_gu = need_grad and not recompute
+    out, g, u = _launch.forward(x2d, wg, wu, fast_accum=fast_accum, save_activations=save_gu)
+    if save_gu:
         ctx.save_for_backward(x2d, wg, wu, g, u)
+    elif need_grad:
+        ctx.save_for_backward(x2d, wg, wu)
     ctx.in_shape = (bs, sq, dm)
     return out.view(bs, sq, di)
 
 
 def swiglu_backward(ctx, grad_output, *, fast_accum: bool):
-    x2d, wg, wu, g, u = ctx.saved_tensors
+    if len(ctx.saved_tensors) == 5:
+        x2d, wg, wu, g, u = ctx.saved_tensors
+    else:
+        x2d, wg, wu = ctx.saved_tensors
+        _, g, u = _launch.forward(x2d, wg, wu, fast_accum=fast_accum, save_activations=True)
     bs, sq, dm = ctx.in_shape
     di = wg.shape[1]
     need_x, need_g, need_u = ctx.needs_input_grad[:3]

@@ -12,11 +12,16 @@ from . import _autograd
 
 
 class FusedSwiGLU(Function):
+    # Set to True to save only x and the weights and recompute x@w_gate, x@w_up in
+    # backward: frees 2*bs*sq*d_intermediate saved elements for one more dual GEMM.
+    recompute_activations = False
+
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.bfloat16)
     def forward(ctx, input: torch.Tensor, weight_gate: torch.Tensor, weight_up: torch.Tensor) -> torch.Tensor:
         assert input.dtype == torch.bfloat16, "Expected torch.bfloat16 inputs and weights."
-        return _autograd.swiglu_forward(ctx, input, weight_gate, weight_up, fast_accum=False)
+        return _autograd.swiglu_forward(ctx, input, weight_gate, weight_up, fast_accum=False,
+                                        recompute=bool(FusedSwiGLU.recompute_activations))
 
     @staticmethod
     @torch.amp.custom_bwd(device_type="cuda")

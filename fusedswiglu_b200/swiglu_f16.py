@@ -16,13 +16,15 @@ from . import _autograd
 
 class FastAccumFusedSwiGLU(Function):
     fast_accum = True
+    recompute_activations = False  # see FusedSwiGLU.recompute_activations
 
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float16)
     def forward(ctx, input: torch.Tensor, weight_gate: torch.Tensor, weight_up: torch.Tensor) -> torch.Tensor:
         assert input.dtype == torch.float16, "Expected torch.float16 inputs and weights."
         ctx.fast_accum = bool(FastAccumFusedSwiGLU.fast_accum)
-        return _autograd.swiglu_forward(ctx, input, weight_gate, weight_up, fast_accum=ctx.fast_accum)
+        return _autograd.swiglu_forward(ctx, input, weight_gate, weight_up, fast_accum=ctx.fast_accum,
+                                        recompute=bool(FastAccumFusedSwiGLU.recompute_activations))
 
     @staticmethod
     @torch.amp.custom_bwd(device_type="cuda")

@@ -509,3 +509,78 @@ def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable():
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
     assert orc.rel_error(host(out), orc.swiglu_ref(inp["x"], inp["w_gate"], inp["w_up"], "bf16")[0]) < 1e-3
+
+
+# ------------------------------------------- memory mode, module, CUDA graphs --
+def test_recompute_mode_gives_bit_identical_gradients():
+    from fused_swiglu import FusedSwiGLU
+
+    torch.manual_seed(7)
+    x, wg, wu = make_input_weights(2, 320, 448, 832)
+    dy = torch.randn(2, 320, 832, device="cuda", dtype=torch.bfloat16)
+    grads = {}
+    for mode in (False, True):
+        FusedSwiGLU.recompute_activations = mode
+        try:
+            x.grad = wg.grad = wu.grad = None
+            out = FusedSwiGLU.apply(x, wg, wu)
+            saved = out.grad_fn.saved_tensors
+            assert len(saved) == (3 if mode else 5)
+            out.backward(dy)
+            grads[mode] = (out.detach().clone(), x.grad.clone(), wg.grad.clone(), wu.grad.clone())
+        finally:
+            FusedSwiGLU.recompute_activations = False
+    for a, b in zip(grads[False], grads[True]):
+        assert torch.equal(a, b)
+
+
+def test_nn_module_wrapper():
+    from fusedswiglu_b200.nn import SwiGLU
+
+    torch.manual_seed(8)
+    m = SwiGLU(256, 512, device="cuda")
+    x = torch.randn(2, 64, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out = m(x)
+    ref = orc.swiglu_ref_torch(x, m.w_gate, m.w_up)
+    assert rel_error(out, ref) < EXPECTED_BF16
+    out.float().pow(2).mean().backward()
+    assert m.w_gate.grad.shape == (256, 512) and x.grad.shape == x.shape
+
+
+def test_forward_backward_can_be_replayed_from_a_cuda_graph():
+    """After one eager warm-up (which does the per-device set-up), a step can be
+    captured in a CUDA graph and replayed on new inputs with identical results."""
+    from fused_swiglu import FusedSwiGLU
+
+    torch.manual_seed(9)
+    bs, sq, dm, di = 1, 128, 512, 1536  # the launch-bound plumbing shape
+    wg = (torch.randn(dm, di, device="cuda", dtype=torch.bfloat16) / math.sqrt(dm)).requires_grad_(True)
+    wu = (torch.randn(dm, di, device="cuda", dtype=torch.bfloat16) / math.sqrt(dm)).requires_grad_(True)
+    static_x = torch.randn(bs, sq, dm, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    static_dy = torch.randn(bs, sq, di, device="cuda", dtype=torch.bfloat16)
+
+    def step():
+        out = FusedSwiGLU.apply(static_x, wg, wu)
+        gx, gg, gu = torch.autograd.grad(out, (static_x, wg, wu), static_dy)
+        return out, gx, gg, gu
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        static_out = step()
+    for seed in (1, 2):
+        gen = torch.Generator(device="cuda").manual_seed(seed)
+        with torch.no_grad():
+            static_x.copy_(torch.randn(bs, sq, dm, device="cuda", dtype=torch.bfloat16, generator=gen))
+            static_dy.copy_(torch.randn(bs, sq, di, device="cuda", dtype=torch.bfloat16, generator=gen))
+        graph.replay()
+        torch.cuda.synchronize()
+        replayed = [t.clone() for t in static_out]
+        eager = step()
+        for a, b in zip(replayed, eager):
+            assert torch.equal(a, b)
