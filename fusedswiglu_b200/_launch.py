@@ -110,3 +110,23 @@ def grad_weights(
         )
     _lib.check("fsw_backward_dw", rc)
     return dwg, dwu
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
+         fast_accum: bool = False) -> torch.Tensor:
+    """C = op(A) @ op(B) for contiguous 2-D 16-bit tensors: A (M,K) or, with trans_a,
+    (K,M); B (K,N) or, with trans_b, (N,K).  fp32 accumulation unless fast_accum (fp16)."""
+    _require_cuda(a, b)
+    assert a.ndim == 2 and b.ndim == 2 and a.dtype == b.dtype, "Expected two 2-D tensors of one dtype"
+    assert not (trans_a and trans_b), "A^T @ B^T is not provided"
+    M, K = (a.shape[1], a.shape[0]) if trans_a else a.shape
+    Kb, N = (b.shape[1], b.shape[0]) if trans_b else b.shape
+    assert K == Kb, f"Dimension mismatch. Expected inner sizes to agree, got {K} and {Kb}"
+    c = torch.empty((M, N), device=a.device, dtype=a.dtype)
+    with torch.cuda.device(a.device):
+        rc = _lib.load().fsw_gemm(
+            a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, int(trans_a), int(trans_b), _code(a),
+            _lib.FSW_ACC_F16 if fast_accum else _lib.FSW_ACC_F32, _stream(a),
+        )
+    _lib.check("fsw_gemm", rc)
+    return c

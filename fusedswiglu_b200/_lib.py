@@ -22,6 +22,7 @@ SIGNATURES = {
     "fsw_backward_dx": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_backward_dw": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_backward": (c_int, [c_void_p] * 11 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
+    "fsw_gemm": (c_int, [c_void_p] * 3 + [c_int64] * 3 + [c_int] * 4 + [c_void_p]),
     "fsw_backward_static_scratch": (c_int, [c_void_p] * 9 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_last_error": (c_char_p, []),
     "fsw_query_device": (c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int64)]),

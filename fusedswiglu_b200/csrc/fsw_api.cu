@@ -123,6 +123,15 @@ static int ensure_device(DeviceInfo** out) {
     FSW_CUDA((prepare_mode<MODE_FWD, 2, 2>()));
     FSW_CUDA((prepare_mode<MODE_DX, 2, 2>()));
     FSW_CUDA((prepare_mode<MODE_DW, 2, 2>()));
+    FSW_CUDA((prepare_mode<MODE_NN, 1, 1>()));
+    FSW_CUDA((prepare_mode<MODE_NT, 1, 1>()));
+    FSW_CUDA((prepare_mode<MODE_TN, 1, 1>()));
+    FSW_CUDA((prepare_mode<MODE_NN, 2, 1>()));
+    FSW_CUDA((prepare_mode<MODE_NT, 2, 1>()));
+    FSW_CUDA((prepare_mode<MODE_TN, 2, 1>()));
+    FSW_CUDA((prepare_mode<MODE_NN, 2, 2>()));
+    FSW_CUDA((prepare_mode<MODE_NT, 2, 2>()));
+    FSW_CUDA((prepare_mode<MODE_TN, 2, 2>()));
     void* sp = nullptr;
     FSW_CUDA(cudaGetSymbolAddress(&sp, g_status_word));
     d.status = static_cast<uint32_t*>(sp);
@@ -278,7 +287,7 @@ struct TileChoice {
 };
 static TileChoice choose_tiles(int mode, int64_t rows, int64_t cols, const DeviceInfo* d) {
   const int want_cg = (int)g_opt.cta_group, want_ns = (int)g_opt.nsub;
-  const int region_n = (mode == MODE_DX) ? 256 : 128;
+  const int region_n = (mode == MODE_FWD || mode == MODE_DW) ? 128 : 256;
   const struct {
     int cg, nsub;
     double speed;
@@ -311,7 +320,7 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   const int cg = tc.cg;
   const int nsub = tc.nsub;
   const int tile_m = 128 * cg;
-  const int tile_n = ((MODE == MODE_DX) ? 256 : 128) * nsub;
+  const int tile_n = ((MODE == MODE_FWD || MODE == MODE_DW) ? 128 : 256) * nsub;
   p.num_m_tiles = (rows + tile_m - 1) / tile_m;
   p.num_n_tiles = (p.N + tile_n - 1) / tile_n;
   p.status = d->status;
@@ -320,8 +329,8 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   p.l2_b = (int)g_opt.l2_b;
   p.wait_limit_ns = (unsigned long long)g_opt.wait_limit_ms * 1000000ull;
   p.stall_producer = (int)g_opt.stall_producer;
-  const int a_major = (MODE == MODE_DW) ? MAJOR_MN : MAJOR_K;
-  const int b_major = (MODE == MODE_DX) ? MAJOR_K : MAJOR_MN;
+  const int a_major = (MODE == MODE_DW || MODE == MODE_TN) ? MAJOR_MN : MAJOR_K;
+  const int b_major = (MODE == MODE_DX || MODE == MODE_NT) ? MAJOR_K : MAJOR_MN;
   fill_operand_desc(a_major, &p.a_desc, &p.a_kadv);
   fill_operand_desc(b_major, &p.b_desc, &p.b_kadv);
   p.idesc = make_idesc(dtype, acc16, a_major, b_major, 128 * cg, 256);
@@ -740,6 +749,58 @@ int fsw_backward(const void* dout, const void* x, const void* w_gate, const void
     return rc;
   return fsw_backward_dw(x, dg_scratch, du_scratch, dw_gate, dw_up, T, dm, di, dtype, accum,
                          stream);
+}
+
+// Plain GEMM C (M,N) = op(A) @ op(B) on row-major 16-bit arrays, for the projection
+// that follows SwiGLU in an MLP block and its two gradients.
+int fsw_gemm(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int trans_a,
+             int trans_b, int dtype, int accum, void* stream) {
+  if (dtype != FSW_BF16 && dtype != FSW_FP16) return fail(FSW_EINVAL, "unknown dtype %d", dtype);
+  if (accum != FSW_ACC_F32 && !(accum == FSW_ACC_F16 && dtype == FSW_FP16))
+    return fail(FSW_EINVAL, "bad accumulate mode %d for dtype %d", accum, dtype);
+  if (trans_a && trans_b) return fail(FSW_EINVAL, "A^T @ B^T is not provided");
+  if (M < 0 || N <= 0 || K < 0 || M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31))
+    return fail(FSW_EINVAL, "bad shape M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  // every row of A, B and C must be a multiple of 16 bytes
+  const int64_t a_inner = trans_a ? M : K, b_inner = trans_b ? K : N;
+  if ((a_inner & 7) || (b_inner & 7) || (N & 7))
+    return fail(FSW_EINVAL, "row lengths (%lld, %lld, %lld) must be multiples of 8",
+                (long long)a_inner, (long long)b_inner, (long long)N);
+  if (M == 0) return FSW_OK;
+  if (!c) return fail(FSW_EINVAL, "NULL pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  DeviceInfo* d = nullptr;
+  int rc = ensure_device(&d);
+  if (rc != FSW_OK) return rc;
+  if (K == 0) {
+    FSW_CUDA(cudaMemsetAsync(c, 0, (size_t)M * N * 2, st));
+    return FSW_OK;
+  }
+  if (!a || !b) return fail(FSW_EINVAL, "NULL pointer");
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c))
+    return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
+  const int mode = trans_a ? MODE_TN : (trans_b ? MODE_NT : MODE_NN);
+  const TileChoice tc = choose_tiles(mode, M, N, d);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  // A: K-major -> rows of 64 k, 128 rows per box; MN-major -> 64 m x 64 k boxes
+  if ((rc = make_map(&p.a0, a, dtype, a_inner, trans_a ? K : M, trans_a ? 64 : 128, "A")) != FSW_OK)
+    return rc;
+  p.a1 = p.a0;
+  // B: K-major (given as (N,K)) -> 256/cg rows per box; MN-major -> 64 n x 64 k boxes
+  if ((rc = make_map(&p.b0, b, dtype, b_inner, trans_b ? N : K, trans_b ? 256 / tc.cg : 64, "B")) !=
+      FSW_OK)
+    return rc;
+  p.b1 = p.b0;
+  p.sg = p.su = p.so = p.a0;
+  p.c0_ptr = c;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.num_k_blocks = (int)((K + 63) / 64);
+  const bool acc16 = accum == FSW_ACC_F16;
+  if (mode == MODE_NN) return run_gemm<MODE_NN>(p, (int)M, dtype, acc16, st, d, tc);
+  if (mode == MODE_NT) return run_gemm<MODE_NT>(p, (int)M, dtype, acc16, st, d, tc);
+  return run_gemm<MODE_TN>(p, (int)M, dtype, acc16, st, d, tc);
 }
 
 // ------------------------------------------------- backward without allocation --

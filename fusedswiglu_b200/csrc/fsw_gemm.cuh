@@ -6,6 +6,11 @@
 //   MODE_DX  : dX = dg @ W_gate^T + du @ W_up^T      (A K-major, B K-major)
 //              one accumulator, the K loop runs over both products
 //   MODE_DW  : [dW_gate | dW_up] = x^T @ [dg | du]   (A MN-major, B MN-major)
+// and, for the projection that follows SwiGLU in an MLP block, three plain
+// single-product GEMMs C = op(A) @ op(B) on row-major arrays:
+//   MODE_NN  : A (M,K) @ B (K,N)      (A K-major,  B MN-major)
+//   MODE_NT  : A (M,K) @ B (N,K)^T    (A K-major,  B K-major)
+//   MODE_TN  : A (K,M)^T @ B (K,N)    (A MN-major, B MN-major)
 //
 // One CTA owns 128 rows x 512 fp32 columns of tensor memory, used as two
 // 256-column accumulator regions.
@@ -36,7 +41,7 @@
 
 namespace fsw {
 
-enum : int { MODE_FWD = 0, MODE_DX = 1, MODE_DW = 2 };
+enum : int { MODE_FWD = 0, MODE_DX = 1, MODE_DW = 2, MODE_NN = 3, MODE_NT = 4, MODE_TN = 5 };
 enum : int { MAJOR_K = 0, MAJOR_MN = 1 };
 
 // Codes written to the status word when a bounded wait gives up.
@@ -100,8 +105,10 @@ constexpr int kSmemBudget = 232448;  // 227 KB opt-in limit per CTA
 template <int MODE, int CG, int NSUB>
 struct TileCfg {
   static_assert(NSUB == 1 || (NSUB == 2 && CG == 2), "512-column tiles need a CTA pair");
-  static constexpr int A_MAJOR = (MODE == MODE_DW) ? MAJOR_MN : MAJOR_K;
-  static constexpr int B_MAJOR = (MODE == MODE_DX) ? MAJOR_K : MAJOR_MN;
+  static constexpr int A_MAJOR = (MODE == MODE_DW || MODE == MODE_TN) ? MAJOR_MN : MAJOR_K;
+  static constexpr int B_MAJOR = (MODE == MODE_DX || MODE == MODE_NT) ? MAJOR_K : MAJOR_MN;
+  // dual: the accumulator columns of a region are [128 from b0 | 128 from b1]
+  static constexpr bool DUAL_B = (MODE == MODE_FWD || MODE == MODE_DW);
   static constexpr int BM = 128;          // accumulator rows per CTA
   static constexpr int BN = 256;          // columns of one accumulator region (MMA N)
   static constexpr int BK = 64;           // one 128-byte swizzle row of 16-bit elements
@@ -124,7 +131,7 @@ struct TileCfg {
   static constexpr int TMEM_COLS = 512;
   static constexpr int NSEG = (MODE == MODE_DX) ? 2 : 1;
   // Output columns covered by one accumulator region / one tile, per output tensor.
-  static constexpr int REGION_N = (MODE == MODE_DX) ? 256 : 128;
+  static constexpr int REGION_N = DUAL_B ? 128 : 256;
   static constexpr int TILE_N = REGION_N * NSUB;
   static constexpr int TILE_M = BM * CG;
   // Arrivals that free one accumulator region.
@@ -397,8 +404,8 @@ __device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& 
 }
 
 // Plain epilogue over 64-column boxes jb in [jb_begin, jb_begin + NJB) of one
-// 256-column region.  MODE_DX: all four boxes belong to c0 at columns n0 + 64*jb;
-// MODE_DW: boxes 0,1 -> c0, boxes 2,3 -> c1, at n0 + 64*(jb&1).  Each box is read,
+// 256-column region.  MODE_DW: boxes 0,1 -> c0, boxes 2,3 -> c1, at n0 + 64*(jb&1);
+// every other mode: all four boxes belong to c0 at columns n0 + 64*jb.  Each box is read,
 // rounded, transposed through the staging buffer and written with row-coalesced
 // stores; `release` is called right after the last tensor-memory read.  (These
 // GEMMs have K loops of 400+ blocks per tile, so the few thousand cycles this
@@ -413,7 +420,7 @@ __device__ __forceinline__ void drain_plain(const GemmParams& p, const EpiCtx& e
 #pragma unroll
     for (int c = 0; c < 4; ++c) load_pack16<T, ACC16>(taddr + jb * 64 + c * 16, &pk[c * 8]);
     if (j == NJB - 1) release();
-    const int col = (MODE == MODE_DX) ? (n0 + jb * 64) : (n0 + (jb & 1) * 64);
+    const int col = (MODE == MODE_DW) ? (n0 + (jb & 1) * 64) : (n0 + jb * 64);
     void* out = (MODE == MODE_DW && jb >= 2) ? p.c1_ptr : p.c0_ptr;
     stage_rows128(e.buf, e.lane, pk);
     __syncwarp();
@@ -550,6 +557,12 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
                 if (C::B_MAJOR == MAJOR_K) {
                   load(dst, seg == 1 ? &p.b1 : &p.b0, k0,
                        n0 + r * C::REGION_N + cta_rank * C::SUB_ROWS);
+                } else if (!C::DUAL_B) {
+                  // one MN-major B: this CTA's SUB_ROWS columns of region r
+#pragma unroll
+                  for (int c = 0; c < C::SUB_ROWS / 64; ++c)
+                    load(dst + c * C::CHUNK_BYTES, &p.b0,
+                         n0 + r * C::REGION_N + cta_rank * C::SUB_ROWS + c * 64, k0);
                 } else if (CG == 1) {
 #pragma unroll
                   for (int c = 0; c < 4; ++c)

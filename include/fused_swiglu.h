@@ -88,6 +88,19 @@ int fsw_backward(const void* dout, const void* x, const void* w_gate, const void
                  int accum, void* stream);
 
 /*
+ * Plain GEMM on row-major 16-bit arrays with the same tcgen05 kernel:
+ *   trans_a = 0, trans_b = 0:  c (M,N) = a (M,K) @ b (K,N)
+ *   trans_a = 0, trans_b = 1:  c (M,N) = a (M,K) @ b (N,K)^T
+ *   trans_a = 1, trans_b = 0:  c (M,N) = a (K,M)^T @ b (K,N)
+ * Every row length (of a, b and c) must be a multiple of 8 elements.  This is the
+ * down projection y = out @ w_down that follows SwiGLU in an MLP block, and its two
+ * gradients.  It has no counterpart in the reference, which stops at `out`
+ * (a user of the reference calls a library GEMM for it).
+ */
+int fsw_gemm(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int trans_a,
+             int trans_b, int dtype, int accum, void* stream);
+
+/*
  * fsw_backward for callers that have no scratch memory to give and may not
  * allocate any.  (No counterpart in the reference, whose launchers allocate
  * fresh dg/du tensors on every call.)
