@@ -76,6 +76,7 @@ class _CudaBackend:
     gate_grad = staticmethod(_launch.gate_grad)
     grad_input = staticmethod(_launch.grad_input)
     grad_weights = staticmethod(_launch.grad_weights)
+    gemm = staticmethod(_launch.gemm)
 
     @staticmethod
     def grad_weights_beside_collective(x2d, dg, du, *, fast_accum=False, world_size=2):
@@ -131,6 +132,64 @@ class ColumnParallelSwiGLU(Function):
         if work is not None:
             work.wait()
         return dx.view(bs, sq, dm), dwg, dwu, None, None, None
+
+
+def shard_rows(w: torch.Tensor, rank: int, world_size: int) -> torch.Tensor:
+    """Contiguous copy of this rank's row slice of a (d_intermediate, d_out) weight -
+    the row-parallel partner of shard_columns for the down projection."""
+    lo, hi = shard_bounds(w.shape[0], rank, world_size)
+    return w[lo:hi].contiguous()
+
+
+class TensorParallelSwiGLUMLP(Function):
+    """``TensorParallelSwiGLUMLP.apply(x, w_gate_shard, w_up_shard, w_down_shard, group=None)``:
+    the whole MLP block ``(silu(x@W_gate) * (x@W_up)) @ W_down`` with the usual
+    column-parallel / row-parallel pairing.  Rank r holds columns of W_gate, W_up
+    and the matching rows of W_down; x is replicated.
+
+    Forward: everything is local up to a partial y, which is all-reduced (one
+    collective).  Backward: dW_down, dout, dg/du, dW_gate, dW_up are local; the
+    partial dX is all-reduced beside the dW GEMM (one collective).  Returns the full
+    y; the gradient for x is the full dX."""
+
+    @staticmethod
+    def forward(ctx, x, w_gate_shard, w_up_shard, w_down_shard, group=None, backend=None):
+        backend = backend or _CudaBackend
+        assert x.ndim == 3 and w_gate_shard.ndim == 2 and w_down_shard.ndim == 2, "Incorrect number of dimensions"
+        assert w_gate_shard.shape == w_up_shard.shape, "Expected both weight matrices to have same shape"
+        assert x.shape[2] == w_gate_shard.shape[0], "Dimension mismatch between x and the weight shards"
+        assert w_gate_shard.shape[1] == w_down_shard.shape[0], "w_down shard must hold the rows matching the column shard"
+        bs, sq, dm = x.shape
+        x2d = x.contiguous().view(bs * sq, dm)
+        wg, wu, wd = w_gate_shard.contiguous(), w_up_shard.contiguous(), w_down_shard.contiguous()
+        out, g, u = backend.forward(x2d, wg, wu, fast_accum=False, save_activations=True)
+        y = backend.gemm(out, wd)
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
+        ctx.save_for_backward(x2d, wg, wu, wd, g, u, out)
+        ctx.meta = (bs, sq, dm, group, backend)
+        return y.view(bs, sq, wd.shape[1])
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x2d, wg, wu, wd, g, u, out = ctx.saved_tensors
+        bs, sq, dm, group, backend = ctx.meta
+        dy = grad_y.contiguous().view(bs * sq, wd.shape[1])
+        dwd = backend.gemm(out, dy, trans_a=True)
+        dout = backend.gemm(dy, wd, trans_b=True)
+        dg, du = backend.gate_grad(dout, g, u)
+        dx = backend.grad_input(dg, du, wg, wu)
+        work = None
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            work = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group, async_op=True)
+        if work is not None and hasattr(backend, "grad_weights_beside_collective"):
+            dwg, dwu = backend.grad_weights_beside_collective(
+                x2d, dg, du, fast_accum=False, world_size=dist.get_world_size(group))
+        else:
+            dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=False)
+        if work is not None:
+            work.wait()
+        return dx.view(bs, sq, dm), dwg, dwu, dwd, None, None
 
 
 def column_parallel_swiglu(

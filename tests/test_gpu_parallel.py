@@ -51,7 +51,27 @@ def _worker(rank, world, port, q):
         def rel(a, b):
             return (torch.linalg.norm(a.float() - b.float()) / torch.linalg.norm(b.float())).item()
 
+        # whole MLP block, tensor parallel vs single GPU
+        from fusedswiglu_b200.mlp import FusedSwiGLUMLP
+
+        wd0 = mk(di, dm) / di ** 0.5
+        dy = mk(bs, sq, dm)
+        xm = x0.clone().requires_grad_(True)
+        wgm = parallel.shard_columns(wg0, rank, world).requires_grad_(True)
+        wum = parallel.shard_columns(wu0, rank, world).requires_grad_(True)
+        wdm = parallel.shard_rows(wd0, rank, world).requires_grad_(True)
+        ym = parallel.TensorParallelSwiGLUMLP.apply(xm, wgm, wum, wdm)
+        ym.backward(dy)
+        xs = x0.clone().requires_grad_(True)
+        wgs, wus, wds = (t.clone().requires_grad_(True) for t in (wg0, wu0, wd0))
+        ys = FusedSwiGLUMLP.apply(xs, wgs, wus, wds)
+        ys.backward(dy)
+        torch.cuda.synchronize()
+        mlp = {"y": rel(ym, ys), "dx": rel(xm.grad, xs.grad), "dwg": rel(wgm.grad, wgs.grad[:, lo:hi]),
+               "dwu": rel(wum.grad, wus.grad[:, lo:hi]), "dwd": rel(wdm.grad, wds.grad[lo:hi])}
+
         q.put((rank, {
+            "mlp": mlp,
             "out_equal": bool(torch.equal(out_full, ref.detach())),
             "dwg_equal": bool(torch.equal(wg.grad, wgr.grad[:, lo:hi])),
             "dwu_equal": bool(torch.equal(wu.grad, wur.grad[:, lo:hi])),
@@ -83,3 +103,6 @@ def test_two_gpu_column_parallel_matches_single_gpu():
         # dX: each rank rounds its partial sum to bf16 before the all-reduce
         assert r["dx_rel"] < 1e-2, (rank, r)
         assert r["status"] == 0
+        # tensor-parallel MLP: partial sums are rounded per rank before the all-reduce
+        for k, v in r["mlp"].items():
+            assert v < 1e-2, (rank, k, r["mlp"])

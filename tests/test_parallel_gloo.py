@@ -40,6 +40,12 @@ class OracleBackend:
     def grad_weights(x2d, dg, du, *, fast_accum=False):
         return (x2d.float().T @ dg.float()).to(x2d.dtype), (x2d.float().T @ du.float()).to(x2d.dtype)
 
+    @staticmethod
+    def gemm(a, b, *, trans_a=False, trans_b=False, fast_accum=False):
+        a32 = a.float().T if trans_a else a.float()
+        b32 = b.float().T if trans_b else b.float()
+        return (a32 @ b32).to(a.dtype)
+
 
 def _free_port():
     with socket.socket() as s:
@@ -108,6 +114,58 @@ def test_two_rank_column_parallel_matches_unsharded_reference():
         assert errs["dx_equal_across_ranks"] == 0.0, (rank, errs)
         for k in ("out", "dx", "dwg", "dwu"):
             assert errs[k] < 1e-2, (rank, k, errs)
+
+
+def _mlp_worker(rank, world, port, q):
+    sys.path.insert(0, str(REPO))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fusedswiglu_b200 import parallel
+
+        torch.manual_seed(1)
+        bs, sq, dm, di = 2, 16, 64, 128
+        x = torch.randn(bs, sq, dm).bfloat16().requires_grad_(True)
+        wg = (torch.randn(dm, di) / dm ** 0.5).bfloat16()
+        wu = (torch.randn(dm, di) / dm ** 0.5).bfloat16()
+        wd = (torch.randn(di, dm) / di ** 0.5).bfloat16()
+        dy = torch.randn(bs, sq, dm).bfloat16()
+        lo, hi = parallel.shard_bounds(di, rank, world)
+        wg_s = parallel.shard_columns(wg, rank, world).requires_grad_(True)
+        wu_s = parallel.shard_columns(wu, rank, world).requires_grad_(True)
+        wd_s = parallel.shard_rows(wd, rank, world).requires_grad_(True)
+        y = parallel.TensorParallelSwiGLUMLP.apply(x, wg_s, wu_s, wd_s, None, OracleBackend)
+        y.backward(dy)
+
+        xr = x.detach().clone().requires_grad_(True)
+        wgr, wur, wdr = (t.clone().requires_grad_(True) for t in (wg, wu, wd))
+        ref = (torch.nn.functional.silu(xr @ wgr) * (xr @ wur)) @ wdr
+        ref.backward(dy)
+
+        def rel(a, b):
+            return (torch.linalg.norm(a.float() - b.float()) / torch.linalg.norm(b.float())).item()
+
+        q.put((rank, {"y": rel(y, ref), "dx": rel(x.grad, xr.grad), "dwg": rel(wg_s.grad, wgr.grad[:, lo:hi]),
+                      "dwu": rel(wu_s.grad, wur.grad[:, lo:hi]), "dwd": rel(wd_s.grad, wdr.grad[lo:hi])}))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_tensor_parallel_mlp_matches_unsharded_reference():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_mlp_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, errs in results:
+        for k, v in errs.items():
+            assert v < 2e-2, (rank, k, errs)
 
 
 def test_shard_bounds_and_errors():
