@@ -19,8 +19,12 @@
 //              tile i+1.
 //   NSUB == 2: a tile is 128 x 512 per CTA and fills both regions; per K block
 //              the A tile is staged once and used by two N=256 MMAs, which cuts
-//              L2->shared-memory traffic per flop by a quarter.  The epilogue is
-//              not overlapped with MMAs, only with the operand prefetch.
+//              L2->shared-memory traffic per flop by a quarter.  There is no
+//              spare tensor memory, so the SwiGLU epilogue first copies its
+//              accumulators (rounded to 16 bits) into registers and releases the
+//              region, then does its math and stores beside the next tile's MMAs;
+//              the plain epilogues are short next to their K loops and are left
+//              un-overlapped.
 // With CG == 2 two CTAs of a cluster form a pair: each stages its own 128 rows
 // of A and half of every B sub-tile; the pair leader issues M=256 x N=256 MMAs
 // that read both CTAs' shared memory and write both CTAs' tensor memory.  No TMA
@@ -32,7 +36,7 @@
 // the buffer back for row-coalesced 16-byte stores, the SwiGLU epilogue hands it to
 // TMA stores).
 //
-// Every mbarrier wait is bounded: after kWaitLimitNs the waiting thread records a
+// Every mbarrier wait is bounded: after the wait limit the waiting thread records a
 // code in `status`, raises the CTA's abort flag and every role leaves its loop;
 // the CTA then lets in-flight copies drain, frees its tensor memory and returns.
 #pragma once
