@@ -24,6 +24,7 @@ SIGNATURES = {
     "fsw_backward": (c_int, [c_void_p] * 11 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_gemm": (c_int, [c_void_p] * 3 + [c_int64] * 3 + [c_int] * 4 + [c_void_p]),
     "fsw_backward_static_scratch": (c_int, [c_void_p] * 9 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
+    "fsw_debug_decode_tile": (c_int, [c_int] * 4 + [POINTER(c_int), POINTER(c_int)]),
     "fsw_last_error": (c_char_p, []),
     "fsw_query_device": (c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int64)]),
     "fsw_status": (c_int64, []),

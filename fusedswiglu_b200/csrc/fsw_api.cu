@@ -751,6 +751,16 @@ int fsw_backward(const void* dout, const void* x, const void* w_gate, const void
                          stream);
 }
 
+// Host copy of the kernels' tile rasterisation, for tests of the scheduling math.
+int fsw_debug_decode_tile(int t, int num_m_tiles, int num_n_tiles, int group_m, int* m_tile,
+                          int* n_tile) {
+  if (!m_tile || !n_tile || num_m_tiles < 1 || num_n_tiles < 1 || group_m < 1 || t < 0 ||
+      (int64_t)t >= (int64_t)num_m_tiles * num_n_tiles)
+    return fail(FSW_EINVAL, "bad tile query");
+  decode_tile_order(t, num_m_tiles, num_n_tiles, group_m, *m_tile, *n_tile);
+  return FSW_OK;
+}
+
 // Plain GEMM C (M,N) = op(A) @ op(B) on row-major 16-bit arrays, for the projection
 // that follows SwiGLU in an MLP block and its two gradients.
 int fsw_gemm(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int trans_a,

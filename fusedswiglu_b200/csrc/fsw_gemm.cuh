@@ -210,14 +210,19 @@ __device__ __forceinline__ bool bounded_wait_warp(uint32_t bar, uint32_t parity,
 
 // Linear tile index -> (m_tile, n_tile); m is grouped so that concurrently
 // running tiles share A row panels and B column panels in L2.
-__device__ __forceinline__ void decode_tile(int t, const GemmParams& p, int& m_tile, int& n_tile) {
-  const int per_group = p.group_m * p.num_n_tiles;
+__host__ __device__ __forceinline__ void decode_tile_order(int t, int num_m_tiles, int num_n_tiles,
+                                                           int group_m, int& m_tile, int& n_tile) {
+  const int per_group = group_m * num_n_tiles;
   const int g = t / per_group;
-  const int first_m = g * p.group_m;
-  const int gsz = min(p.num_m_tiles - first_m, p.group_m);
+  const int first_m = g * group_m;
+  const int rest = num_m_tiles - first_m;
+  const int gsz = rest < group_m ? rest : group_m;
   const int r = t - g * per_group;
   m_tile = first_m + r % gsz;
   n_tile = r / gsz;
+}
+__device__ __forceinline__ void decode_tile(int t, const GemmParams& p, int& m_tile, int& n_tile) {
+  decode_tile_order(t, p.num_m_tiles, p.num_n_tiles, p.group_m, m_tile, n_tile);
 }
 
 // ---------------------------------------------------------------- epilogue --

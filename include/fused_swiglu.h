@@ -164,6 +164,14 @@ int64_t fsw_status(void);
 int fsw_set_option(const char* name, int64_t value);
 int64_t fsw_get_option(const char* name);
 
+/*
+ * Testing aid (runs on the host, needs no GPU): the (m_tile, n_tile) that the
+ * kernels' rasterisation assigns to linear tile index t for a grid of
+ * num_m_tiles x num_n_tiles tiles issued group_m rows at a time.
+ */
+int fsw_debug_decode_tile(int t, int num_m_tiles, int num_n_tiles, int group_m, int* m_tile,
+                          int* n_tile);
+
 #ifdef __cplusplus
 }
 #endif

@@ -78,3 +78,21 @@ def test_options_roundtrip():
         assert _lib.get_option(name) == 0  # 0 = chosen per launch
     with pytest.raises(_lib.FusedSwiGLUError):
         _lib.set_option("nsub", 3)
+
+
+def test_tile_rasterisation_visits_every_tile_exactly_once():
+    """The grouped tile order used by the kernels is a permutation of the tile grid
+    for ragged group sizes too, and walks group_m rows before the column advances."""
+    lib = _lib.load()
+    m, n = ctypes.c_int(), ctypes.c_int()
+    for num_m, num_n, gm in [(1, 1, 1), (5, 3, 2), (7, 4, 16), (16, 56, 16), (128, 8, 2), (33, 9, 8), (3, 1, 5)]:
+        seen = []
+        for t in range(num_m * num_n):
+            assert lib.fsw_debug_decode_tile(t, num_m, num_n, gm, ctypes.byref(m), ctypes.byref(n)) == 0
+            assert 0 <= m.value < num_m and 0 <= n.value < num_n
+            seen.append((m.value, n.value))
+        assert len(set(seen)) == num_m * num_n, (num_m, num_n, gm)
+        # the first min(gm, num_m) tiles share column 0 and have consecutive rows
+        first = min(gm, num_m)
+        assert seen[:first] == [(i, 0) for i in range(first)]
+    assert lib.fsw_debug_decode_tile(99, 3, 3, 1, ctypes.byref(m), ctypes.byref(n)) == -1
