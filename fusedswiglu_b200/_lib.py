@@ -6,7 +6,7 @@ an exception is raised.  There is no PyTorch or CPU fallback.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_int, c_int64, c_void_p, POINTER
+from ctypes import c_char_p, c_int, c_int64, c_uint32, c_uint64, c_void_p, POINTER
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libfused_swiglu_sm100.so"
@@ -25,6 +25,7 @@ SIGNATURES = {
     "fsw_gemm": (c_int, [c_void_p] * 3 + [c_int64] * 3 + [c_int] * 4 + [c_void_p]),
     "fsw_backward_static_scratch": (c_int, [c_void_p] * 9 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_debug_decode_tile": (c_int, [c_int] * 4 + [POINTER(c_int), POINTER(c_int)]),
+    "fsw_debug_descriptors": (c_int, [c_int] * 6 + [POINTER(c_uint32), POINTER(c_uint64), POINTER(c_uint64)]),
     "fsw_last_error": (c_char_p, []),
     "fsw_query_device": (c_int, [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int64)]),
     "fsw_status": (c_int64, []),

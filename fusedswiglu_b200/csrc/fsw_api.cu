@@ -761,6 +761,19 @@ int fsw_debug_decode_tile(int t, int num_m_tiles, int num_n_tiles, int group_m, 
   return FSW_OK;
 }
 
+// The descriptor constants a launch would use, for known-answer tests of the encoders.
+int fsw_debug_descriptors(int dtype, int accum, int a_major, int b_major, int m, int n,
+                          uint32_t* idesc, uint64_t* sdesc_k_major, uint64_t* sdesc_mn_major) {
+  if ((dtype != FSW_BF16 && dtype != FSW_FP16) || (a_major | b_major) >> 1 || !idesc ||
+      !sdesc_k_major || !sdesc_mn_major)
+    return fail(FSW_EINVAL, "bad descriptor query");
+  *idesc = make_idesc(dtype, accum == FSW_ACC_F16, a_major, b_major, m, n);
+  uint32_t kadv = 0;
+  fill_operand_desc(MAJOR_K, sdesc_k_major, &kadv);
+  fill_operand_desc(MAJOR_MN, sdesc_mn_major, &kadv);
+  return FSW_OK;
+}
+
 // Plain GEMM C (M,N) = op(A) @ op(B) on row-major 16-bit arrays, for the projection
 // that follows SwiGLU in an MLP block and its two gradients.
 int fsw_gemm(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int trans_a,

@@ -172,6 +172,14 @@ int64_t fsw_get_option(const char* name);
 int fsw_debug_decode_tile(int t, int num_m_tiles, int num_n_tiles, int group_m, int* m_tile,
                           int* n_tile);
 
+/*
+ * Testing aid (host only): the tcgen05 instruction descriptor for the given types,
+ * operand majorness (0 = K-major, 1 = MN-major) and MMA shape, and the two
+ * shared-memory matrix descriptors (without start address) the kernels use.
+ */
+int fsw_debug_descriptors(int dtype, int accum, int a_major, int b_major, int m, int n,
+                          uint32_t* idesc, uint64_t* sdesc_k_major, uint64_t* sdesc_mn_major);
+
 #ifdef __cplusplus
 }
 #endif

@@ -96,3 +96,32 @@ def test_tile_rasterisation_visits_every_tile_exactly_once():
         first = min(gm, num_m)
         assert seen[:first] == [(i, 0) for i in range(first)]
     assert lib.fsw_debug_decode_tile(99, 3, 3, 1, ctypes.byref(m), ctypes.byref(n)) == -1
+
+
+def test_descriptor_encoders_known_answers():
+    """Bit layouts of the tcgen05 descriptors, checked against values assembled by
+    hand from the documented fields.  Instruction descriptor (kind::f16): D format
+    at bit 4 (1 = fp32), A/B format at bits 7/10 (1 = bf16, 0 = fp16), A/B major at
+    bits 15/16 (1 = MN-major), N>>3 at bit 17, M>>4 at bit 24.  Shared-memory
+    descriptor: leading byte offset >>4 at bit 16, stride byte offset >>4 at bit 32,
+    version 1 at bit 46, layout type 2 (128-byte swizzle) at bit 61."""
+    lib = _lib.load()
+    idesc, sk, smn = ctypes.c_uint32(), ctypes.c_uint64(), ctypes.c_uint64()
+
+    def q(dtype, accum, a_major, b_major, m, n):
+        assert lib.fsw_debug_descriptors(dtype, accum, a_major, b_major, m, n, ctypes.byref(idesc),
+                                         ctypes.byref(sk), ctypes.byref(smn)) == 0
+        return idesc.value
+
+    # forward: bf16, fp32 acc, A K-major, B MN-major, CTA pair M=256, N=256
+    assert q(0, 0, 0, 1, 256, 256) == (1 << 4) | (1 << 7) | (1 << 10) | (1 << 16) | (32 << 17) | (16 << 24)
+    # dX: both K-major
+    assert q(0, 0, 0, 0, 256, 256) == (1 << 4) | (1 << 7) | (1 << 10) | (32 << 17) | (16 << 24)
+    # dW: both MN-major, single CTA M=128
+    assert q(0, 0, 1, 1, 128, 256) == (1 << 4) | (1 << 7) | (1 << 10) | (3 << 15) | (32 << 17) | (8 << 24)
+    # fp16 with fp16 accumulator: all format fields zero
+    assert q(1, 1, 0, 1, 256, 256) == (1 << 16) | (32 << 17) | (16 << 24)
+    # K-major: LBO 16 B (ignored with swizzle), SBO 1024 B; MN-major: LBO 8192 B, SBO 1024 B
+    assert sk.value == (1 << 16) | (64 << 32) | (1 << 46) | (2 << 61)
+    assert smn.value == (512 << 16) | (64 << 32) | (1 << 46) | (2 << 61)
+    assert lib.fsw_debug_descriptors(5, 0, 0, 0, 128, 256, ctypes.byref(idesc), ctypes.byref(sk), ctypes.byref(smn)) == -1
