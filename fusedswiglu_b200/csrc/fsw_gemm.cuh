@@ -73,6 +73,7 @@ struct GemmParams {
   int num_k_blocks;        // 64-wide K blocks per product
   int store_gu;            // MODE_FWD: also write g and u
   int l2_a, l2_b;          // L2 eviction priority of A / B loads: 0 normal, 1 first, 2 last
+  int l2_out;              // same for the forward's output stores
   uint32_t* status;        // device status word (0 = ok)
   void *c0_ptr, *c1_ptr, *c2_ptr;  // outputs (see the mode table above); row stride N
   unsigned long long* clk_probe;   // [2]: SM cycles and nanoseconds CTA 0 was resident
@@ -368,6 +369,7 @@ __device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& 
                                              int n0, int jb_begin, Release release) {
   const uint32_t buf0 = e.buf, buf1 = e.buf + 2048u;
   const bool rows_ok = e.row0 < p.M;
+  const uint64_t pol_out = ptx::make_l2_policy(p.l2_out);
   uint32_t G[NJB * 32], U[NJB * 32];
 #pragma unroll
   for (int c = 0; c < NJB * 4; ++c)
@@ -388,8 +390,8 @@ __device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& 
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (e.lane == 0 && in_range) {
-        ptx::tma_store_2d(&p.sg, buf0, col, e.row0);
-        ptx::tma_store_2d(&p.su, buf1, col, e.row0);
+        ptx::tma_store_2d_hint(&p.sg, buf0, col, e.row0, pol_out);
+        ptx::tma_store_2d_hint(&p.su, buf1, col, e.row0, pol_out);
         ptx::tma_store_commit();
       }
     }
@@ -406,7 +408,7 @@ __device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& 
     ptx::fence_proxy_async_smem();
     __syncwarp();
     if (e.lane == 0 && in_range) {
-      ptx::tma_store_2d(&p.so, buf0, col, e.row0);
+      ptx::tma_store_2d_hint(&p.so, buf0, col, e.row0, pol_out);
       ptx::tma_store_commit();
     }
   }

@@ -133,6 +133,14 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src_smem
                ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src_smem), "r"(x), "r"(y)
                : "memory");
 }
+// Same with an L2 eviction-priority policy for the written lines.
+__device__ __forceinline__ void tma_store_2d_hint(const void* tmap, uint32_t src_smem, int32_t x,
+                                                  int32_t y, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+      ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src_smem), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
