@@ -42,7 +42,11 @@ struct Options {
   int64_t wait_limit_ms = 2000;  // bound on every device-side wait
   int64_t stall_producer = 0;    // test hook: make the consumers' waits run out
   int64_t gemm_max_sms = 0;      // cap on SMs a GEMM launch occupies (0 = all of them)
-  int64_t l2_a = 0, l2_b = 0;    // L2 eviction priority of A / B operand loads (0/1/2)
+  int64_t l2_a = 2, l2_b = 2;    // L2 eviction priority of A / B operand loads (0 normal,
+                                 // 1 first, 2 last).  Evict-last keeps operand panels, which
+                                 // other CTAs of the wave are about to read, ahead of output
+                                 // lines: +1.5-3.6 % forward, +1-3 % dX and dW in round-robin
+                                 // A/B runs at the power cap.
   int64_t l2_out = 1;            // ... of the forward's g/u/out stores: evict first, they are
                                  // not read again by this launch (measured: 5 % fewer DRAM
                                  // reads, +1.2 % sustained forward throughput)
@@ -346,19 +350,25 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   if (g_opt.gemm_max_sms > 0 && g_opt.gemm_max_sms < avail_sms) avail_sms = (int)g_opt.gemm_max_sms;
   // Rasterisation: tiles are issued group_m rows at a time, sweeping the columns.
   // The tiles in flight then form roughly a group_m x (workers / group_m) block and
-  // re-read group_m A panels + that many B panels from HBM per wave.  Measured DRAM
-  // reads on B200 (Llama-3-8B shape) are lowest at 16 rows when there are many
-  // column tiles (forward, dW) and at 2-4 rows when all column tiles of the problem
-  // fit in flight at once (dX: 8 column tiles of 512), where every wave streams all
-  // of B anyway.
+  // re-read group_m A panels + that many B panels from HBM per wave.  The GPU runs
+  // at its power cap, so HBM traffic saved comes back as SM clock: a poor group
+  // height costs up to 25 % of throughput.  The rule below is fitted to sweeps of
+  // group_m on B200 over the Llama-3-8B and -70B MLP shapes and their 1/2, 1/4 and
+  // 1/8 column shards:
+  //   - at most 9 column tiles (dX of d_model 4096; an 8-way shard): every wave
+  //     streams nearly all of B anyway, 1-2 rows are best;
+  //   - at most 32 row tiles (dW, whose rows are d_model): one group over all rows;
+  //   - otherwise 16 rows, or 24 when the reduction is deeper than 4096.
   {
     const int workers = (cg == 2) ? avail_sms / 2 : avail_sms;
     int gm = (int)g_opt.group_m;
     if (gm < 1) {
-      if (p.num_n_tiles * 4 <= workers) {
+      if (p.num_n_tiles * 8 <= workers) {
         gm = workers / (p.num_n_tiles * 4);
+      } else if (p.num_m_tiles <= 32) {
+        gm = p.num_m_tiles;
       } else {
-        gm = 16;
+        gm = p.num_k_blocks <= 64 ? 16 : 24;
       }
     }
     if (gm < 1) gm = 1;

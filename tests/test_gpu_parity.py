@@ -195,7 +195,7 @@ def test_reference_backward_suite():
 
 @pytest.mark.parametrize("opts", [
     {"cta_group": 1, "nsub": 1}, {"cta_group": 2, "nsub": 1}, {"cta_group": 2, "nsub": 2},
-    {"gemm_max_sms": 100}, {"gemm_max_sms": 3}, {"group_m": 1}, {"group_m": 5}, {"l2_a": 2}, {"l2_out": 0},
+    {"gemm_max_sms": 100}, {"gemm_max_sms": 3}, {"group_m": 1}, {"group_m": 5}, {"group_m": 24}, {"l2_a": 0}, {"l2_b": 0}, {"l2_out": 0},
 ])
 def test_tile_and_scheduling_options_do_not_change_results(opts):
     """Every tile shape / rasterisation / SM-cap setting computes the same GEMMs, so
