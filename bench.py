@@ -79,6 +79,8 @@ def parse_args():
                     help="library tuning knob passed to fsw_set_option, e.g. --opt group_m=16 (repeatable)")
     ap.add_argument("--only", default=None, choices=["fwd", "ew", "dx", "dw"],
                     help="launch only this kernel in each step (for profiling one kernel); prints no bench line")
+    ap.add_argument("--shard-of", type=int, default=1, metavar="N",
+                    help="with --only on one GPU: time rank 0's 1/N column shard of the workload")
     return ap.parse_args()
 
 
@@ -250,7 +252,12 @@ def run_ours(args):
     fast = dtype == "fp16" and not args.fp32_accum  # fp16 accumulator in forward and dW
     FastAccumFusedSwiGLU.fast_accum = fast
     T = bs * sq
-    lo, hi = parallel.shard_bounds(di, rank, world)
+    if args.shard_of > 1:
+        if not args.only or world != 1:
+            raise SystemExit("--shard-of needs --only and a single GPU")
+        lo, hi = parallel.shard_bounds(di, 0, args.shard_of)
+    else:
+        lo, hi = parallel.shard_bounds(di, rank, world)
     di_local = hi - lo
     K, W = args.steps, max(args.warmup, 3)
 
