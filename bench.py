@@ -72,6 +72,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-gpu-bar", action="store_true",
+                    help="skip timing torch's own CUDA SwiGLU (cuBLAS + eager kernels) on the same GPU")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--fp32-accum", action="store_true",
                     help="fp16 workloads: accumulate in fp32 instead of the fp16 accumulator")
@@ -361,6 +363,7 @@ def run_ours(args):
     status = _lib.device_status()
     if status != 0:
         raise SystemExit(f"a kernel gave up on a bounded wait (status {status}); no number reported")
+    pacing = {"pace_kb": _lib.get_option("pace_kb"), "switched_off_in_last_launch": _lib.get_option("pace_off")}
     ms_per_step = total_ms / K
     total_flops = flops_per_step(T, dm, di)  # whole job, all ranks
     value = total_flops / ms_per_step / 1e9
@@ -460,6 +463,36 @@ def run_ours(args):
         if status != 0:
             raise SystemExit(f"a kernel gave up on a bounded wait (status {status}) in the end-to-end loop")
 
+    # ---- same-box bar: the reference test's oracle expression on this GPU through
+    # torch (two cuBLAS GEMMs + eager silu/mul, autograd backward).  Library code, timed
+    # after everything above so that it cannot disturb the numbers reported as ours.
+    gpu_bar = None
+    if world == 1 and not args.no_gpu_bar:
+        xr = x.detach().clone().requires_grad_(True)
+        wgr = wg.detach().clone().requires_grad_(True)
+        wur = wu.detach().clone().requires_grad_(True)
+
+        def bar_step():
+            xr.grad = wgr.grad = wur.grad = None
+            o = torch.nn.functional.silu(xr @ wgr) * (xr @ wur)
+            o.backward(dout)
+
+        for _ in range(3):
+            bar_step()
+        n_bar = max(3, min(K, 10))
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        b0.record()
+        for _ in range(n_bar):
+            bar_step()
+        b1.record()
+        torch.cuda.synchronize()
+        bar_ms = b0.elapsed_time(b1) / n_bar
+        gpu_bar = {"value": total_flops / bar_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": bar_ms, "steps": n_bar,
+                   "what": "torch CUDA silu(x@W_gate)*(x@W_up) + autograd backward on the same GPU "
+                           "(cuBLAS GEMMs + eager elementwise kernels); a library bar, not this repo's code"}
+        del xr, wgr, wur
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -512,6 +545,7 @@ def run_ours(args):
                    "l2": "inputs larger than L2 (activations and weights exceed 126 MB); no flush",
                    "comm_sms_reserved_during_dw": parallel.comm_sms(world) if world > 1 else 0,
                    "accumulate": "fp16 accumulator in forward and dW, fp32 in dX" if fast else "fp32", "tile_options": {k: _lib.get_option(k) for k in ("cta_group", "nsub", "group_m")},
+                   "producer_pacing": pacing,
                    "tile_note": "0 = chosen per launch; this workload gets CTA pairs, 256x512 tiles"},
         "frac_of_nominal_bf16_peak": value / (NOMINAL_BF16_TFLOPS * world),
         "frac_of_measured_sustained": value / (peaks["bf16_tflops_sustained"] * world),
@@ -521,6 +555,7 @@ def run_ours(args):
         "roofline": roofline,
         "e2e": e2e,
         "cpu_baseline": cpu_baseline,
+        "gpu_library_bar": gpu_bar,
     }
     print(json.dumps(line), flush=True)
     if world > 1:

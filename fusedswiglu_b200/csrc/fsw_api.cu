@@ -50,6 +50,11 @@ struct Options {
   int64_t l2_out = 1;            // ... of the forward's g/u/out stores: evict first, they are
                                  // not read again by this launch (measured: 5 % fewer DRAM
                                  // reads, +1.2 % sustained forward throughput)
+  int64_t l2_promo = 2;          // TMA L2 promotion of operand and output maps: 0 none,
+                                 // 1 = 128 bytes, 2 = 256 bytes
+  int64_t pace_kb = 32;          // producers of all CTAs meet every pace_kb K blocks so that
+                                 // the two dies keep sharing operand panels in L2 (0 = off)
+  int64_t pace_limit_us = 50;    // longest wait at one meeting point
   int64_t ew_blocks_per_sm = 32;  // grid cap of the elementwise kernel, per SM
   // Debug overrides of the UMMA shared-memory descriptor fields (0 = built-in).
   int64_t k_lbo = 0, k_sbo = 0, k_kadv = 0;
@@ -59,6 +64,8 @@ static Options g_opt;
 
 // Status word the kernels write when a bounded wait gives up.
 __device__ uint32_t g_status_word;
+// Arrival counter and off switch of the producers' pacing (see Pacer).
+__device__ unsigned int g_pace[2];
 // SM cycles and nanoseconds that CTA 0 of the last GEMM launch was resident.
 __device__ unsigned long long g_clk_probe[8];
 
@@ -71,6 +78,7 @@ struct DeviceInfo {
   int max_pairs = 0;  // co-resident 2-CTA clusters of the GEMM kernels
   uint32_t* status = nullptr;
   unsigned long long* clk_probe = nullptr;
+  unsigned int* pace = nullptr;
 };
 static DeviceInfo g_dev[kMaxDevices];
 static std::mutex g_mu;
@@ -144,6 +152,8 @@ static int ensure_device(DeviceInfo** out) {
     d.status = static_cast<uint32_t*>(sp);
     FSW_CUDA(cudaGetSymbolAddress(&sp, g_clk_probe));
     d.clk_probe = static_cast<unsigned long long*>(sp);
+    FSW_CUDA(cudaGetSymbolAddress(&sp, g_pace));
+    d.pace = static_cast<unsigned int*>(sp);
     // How many CTA pairs can be resident at once (a GPC with an odd SM count
     // leaves one SM without a partner).
     {
@@ -186,7 +196,9 @@ static int make_map(CUtensorMap* m, const void* ptr, int dtype, uint64_t inner, 
       m, dtype == FSW_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
       const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
       box_inner == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
-      CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      g_opt.l2_promo == 0   ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+      : g_opt.l2_promo == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                            : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(FSW_ECUDA, "cuTensorMapEncodeTiled(%s: inner=%llu outer=%llu box_outer=%u) -> %d",
@@ -350,30 +362,52 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   if (g_opt.gemm_max_sms > 0 && g_opt.gemm_max_sms < avail_sms) avail_sms = (int)g_opt.gemm_max_sms;
   // Rasterisation: tiles are issued group_m rows at a time, sweeping the columns.
   // The tiles in flight then form roughly a group_m x (workers / group_m) block and
-  // re-read group_m A panels + that many B panels from HBM per wave.  The GPU runs
-  // at its power cap, so HBM traffic saved comes back as SM clock: a poor group
-  // height costs up to 25 % of throughput.  The rule below is fitted to sweeps of
-  // group_m on B200 over the Llama-3-8B and -70B MLP shapes and their 1/2, 1/4 and
-  // 1/8 column shards:
+  // read group_m A panels (256 rows each) + that many B panels (512 rows each) from
+  // HBM per wave; with the producers paced (see Pacer) measured DRAM reads match
+  // this count.  The GPU runs at its power cap, so HBM traffic saved comes back as
+  // SM clock: a poor group height costs up to 25 % of throughput.
   //   - at most 9 column tiles (dX of d_model 4096; an 8-way shard): every wave
   //     streams nearly all of B anyway, 1-2 rows are best;
-  //   - at most 32 row tiles (dW, whose rows are d_model): one group over all rows;
-  //   - otherwise 16 rows, or 24 when the reduction is deeper than 4096.
+  //   - otherwise the height that makes the block square in elements,
+  //     sqrt(2 * workers) = 12 for 74 CTA pairs of 256x512 tiles, adjusted so that the groups are of
+  //     equal height; one group if that is at most 1.5 heights (dW, whose rows are
+  //     d_model).
+  // Checked by sweeps of group_m on the Llama-3-8B and -70B MLP shapes and their
+  // 1/2, 1/4, 1/8 column shards.
   {
     const int workers = (cg == 2) ? avail_sms / 2 : avail_sms;
     int gm = (int)g_opt.group_m;
     if (gm < 1) {
       if (p.num_n_tiles * 8 <= workers) {
         gm = workers / (p.num_n_tiles * 4);
-      } else if (p.num_m_tiles <= 32) {
-        gm = p.num_m_tiles;
       } else {
-        gm = p.num_k_blocks <= 64 ? 16 : 24;
+        const int aspect = (cg == 2 && nsub == 1) ? 1 : 2;  // tile columns / tile rows
+        int g0 = 1;
+        while ((g0 + 1) * (g0 + 1) <= aspect * workers) ++g0;  // floor(sqrt(aspect * workers))
+        if (2 * p.num_m_tiles <= 3 * g0) {
+          gm = p.num_m_tiles;
+        } else {
+          const int groups = (p.num_m_tiles + g0 / 2) / g0;
+          gm = (p.num_m_tiles + groups - 1) / groups;
+        }
       }
     }
     if (gm < 1) gm = 1;
     if (gm > p.num_m_tiles) gm = p.num_m_tiles;
     p.group_m = gm;
+  }
+  // Pacing only pays when the launch runs several waves of tiles on most of the GPU.
+  p.pace = nullptr;
+  p.pace_kb = 0;
+  p.pace_limit_ns = (unsigned int)(g_opt.pace_limit_us * 1000);
+  {
+    const long long workers = (cg == 2) ? avail_sms / 2 : avail_sms;
+    if (g_opt.pace_kb > 0 && tiles > workers) {
+      p.pace = d->pace;
+      p.pace_kb = (int)g_opt.pace_kb;
+      e = cudaMemsetAsync(d->pace, 0, 2 * sizeof(unsigned int), st);
+      if (e != cudaSuccess) return fail(FSW_ECUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(e));
+    }
   }
   if (cg == 2) {
     int max_pairs = d->max_pairs < avail_sms / 2 ? d->max_pairs : avail_sms / 2;
@@ -560,6 +594,15 @@ int fsw_set_option(const char* name, int64_t value) {
   } else if (!strcmp(name, "l2_a") || !strcmp(name, "l2_b") || !strcmp(name, "l2_out")) {
     if (value < 0 || value > 2) return fail(FSW_EINVAL, "%s must be 0, 1 or 2", name);
     (name[3] == 'a' ? g_opt.l2_a : name[3] == 'b' ? g_opt.l2_b : g_opt.l2_out) = value;
+  } else if (!strcmp(name, "pace_kb")) {
+    if (value < 0 || value > (1 << 20)) return fail(FSW_EINVAL, "pace_kb must be >= 0 (0 = no pacing)");
+    g_opt.pace_kb = value;
+  } else if (!strcmp(name, "pace_limit_us")) {
+    if (value < 1 || value > 100000) return fail(FSW_EINVAL, "pace_limit_us must be in [1, 100000]");
+    g_opt.pace_limit_us = value;
+  } else if (!strcmp(name, "l2_promo")) {
+    if (value < 0 || value > 2) return fail(FSW_EINVAL, "l2_promo must be 0, 1 or 2");
+    g_opt.l2_promo = value;
   } else if (!strcmp(name, "ew_blocks_per_sm")) {
     if (value < 1 || value > 64) return fail(FSW_EINVAL, "ew_blocks_per_sm must be in [1, 64]");
     g_opt.ew_blocks_per_sm = value;
@@ -593,6 +636,18 @@ int64_t fsw_get_option(const char* name) {
   if (!strcmp(name, "l2_a")) return g_opt.l2_a;
   if (!strcmp(name, "l2_b")) return g_opt.l2_b;
   if (!strcmp(name, "l2_out")) return g_opt.l2_out;
+  if (!strcmp(name, "l2_promo")) return g_opt.l2_promo;
+  if (!strcmp(name, "pace_kb")) return g_opt.pace_kb;
+  if (!strcmp(name, "pace_limit_us")) return g_opt.pace_limit_us;
+  if (!strcmp(name, "pace_off")) {
+    // 1 if the last paced launch on the current device switched its pacing off; synchronises
+    DeviceInfo* d = nullptr;
+    if (ensure_device(&d) != FSW_OK) return -1;
+    unsigned int v[2] = {0, 0};
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpy(v, d->pace, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return v[1];
+  }
   if (!strcmp(name, "k_lbo")) return g_opt.k_lbo;
   if (!strcmp(name, "k_sbo")) return g_opt.k_sbo;
   if (!strcmp(name, "k_kadv")) return g_opt.k_kadv;

@@ -80,6 +80,11 @@ struct GemmParams {
   unsigned long long wait_limit_ns;  // every mbarrier wait gives up after this long
   int stall_producer;              // test hook: the TMA producer issues nothing, so the
                                    // consumers' bounded waits run out and the error path runs
+  // Advisory pacing of the TMA producers (nullptr or pace_kb 0 = free-running):
+  // pace[0] counts arrivals, pace[1] != 0 switches pacing off for the launch.
+  unsigned int* pace;
+  int pace_kb;                     // K blocks between two meeting points
+  unsigned int pace_limit_ns;      // longest a producer waits at a meeting point
 };
 
 // Epilogue warps: 4 (one per TMEM lane quadrant) or 8 (two per quadrant).
@@ -208,6 +213,46 @@ __device__ __forceinline__ bool bounded_wait_warp(uint32_t bar, uint32_t parity,
                                                   const AbortCtl& ctl, uint32_t code) {
   return __all_sync(0xffffffffu, bounded_wait_thread(bar, parity, ctl, code));
 }
+
+// Advisory pacing.  The SMs of the two dies of a B200 do not run this kernel at
+// exactly the same speed (measured: 1.5-3 % apart), so the CTAs of one die pull
+// ahead by a few microseconds per tile.  Once the lead exceeds the time a line
+// survives in L2 (about 50 us at the rates this kernel streams) the two dies stop
+// sharing operand panels and every panel is fetched from HBM twice.  The producers
+// therefore meet every pace_kb K blocks: each adds 1 to a counter and waits until
+// all CTAs that work on the same wave of tiles have done so.  The meeting carries
+// no data and is not needed for correctness.  A wait ends after pace_limit_ns at
+// the latest and the CTA goes on (it has been counted, so later meetings still
+// work); a CTA whose waits ran out three times switches pacing off for the whole
+// launch (pace[1]).  CTAs that are late or not resident (SMs taken by another
+// kernel) therefore cost a few short waits, never a hang and never an error.
+struct Pacer {
+  unsigned int* ctr;
+  int kb;
+  unsigned int limit_ns;
+  bool on;
+  int misses;
+  __device__ __forceinline__ void meet(unsigned int target, const AbortCtl& ctl) {
+    atomicAdd(ctr, 1u);
+    volatile unsigned int* v = ctr;
+    if (v[0] >= target) return;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    for (;;) {
+      if (v[0] >= target) return;
+      if (v[1] != 0u || *ctl.flag != 0u) {
+        on = false;
+        return;
+      }
+      if (ptx::globaltimer_ns() - t0 > limit_ns) {
+        if (++misses >= 3) {
+          v[1] = 1u;
+          on = false;
+        }
+        return;
+      }
+    }
+  }
+};
 
 // Linear tile index -> (m_tile, n_tile); m is grouped so that concurrently
 // running tiles share A row panels and B column panels in L2.
@@ -523,13 +568,28 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
       bool ok = true;
       const uint64_t pol_a = ptx::make_l2_policy(p.l2_a);
       const uint64_t pol_b = ptx::make_l2_policy(p.l2_b);
+      Pacer pacer{p.pace, p.pace_kb, p.pace_limit_ns, p.pace != nullptr && p.pace_kb > 0, 0};
+      const int kb_per_tile = C::NSEG * num_kb;
+      const unsigned int meets_per_tile =
+          pacer.on ? static_cast<unsigned int>((kb_per_tile + pacer.kb - 1) / pacer.kb) : 0u;
       for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
         int m_tile, n_tile;
         decode_tile(t, p, m_tile, n_tile);
         const int m0 = m_tile * C::TILE_M + cta_rank * C::BM;
         const int n0 = n_tile * C::TILE_N;
+        // Every wave before this one was full; this one has `in_wave` CTAs.
+        const int wave = (t - cluster_id) / num_clusters;
+        const int left = num_tiles - wave * num_clusters;
+        const unsigned int in_wave = static_cast<unsigned int>((left < num_clusters ? left : num_clusters) * CG);
+        const unsigned int before = static_cast<unsigned int>(wave) * meets_per_tile * gridDim.x;
+        int until_meet = 0;
+        unsigned int meet_no = 0;
         for (int seg = 0; seg < C::NSEG && ok; ++seg) {
           for (int kb = 0; kb < num_kb; ++kb) {
+            if (pacer.on && --until_meet < 0) {
+              until_meet = pacer.kb - 1;
+              pacer.meet(before + (++meet_no) * in_wave, ctl);
+            }
             ok = bounded_wait_thread(empty_bar(s), ph ^ 1u, ctl, WAIT_PRODUCER_EMPTY);
             if (!ok) break;
             const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;

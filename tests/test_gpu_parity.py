@@ -216,6 +216,38 @@ def test_tile_and_scheduling_options_do_not_change_results(opts):
         assert np.array_equal(got[k], base[k]), (opts, k)
 
 
+@pytest.mark.parametrize("opts", [
+    {"pace_kb": 1}, {"pace_kb": 5}, {"pace_kb": 32, "pace_limit_us": 1},
+    {"pace_kb": 3, "cta_group": 2, "nsub": 2}, {"pace_kb": 2, "cta_group": 2, "nsub": 1},
+    {"pace_kb": 7, "gemm_max_sms": 50},
+])
+def test_producer_pacing_does_not_change_results(opts):
+    """The producers' meeting points are advisory: with any spacing, with waits that
+    run out at once (1 us limit) and on several waves of tiles with a ragged last
+    wave, results are bit-identical to the free-running kernel and no error is
+    recorded."""
+    from fusedswiglu_b200 import _lib
+
+    inp = orc.make_inputs(1, 4224, 512, 2304, "bf16", seed=33, dout_std=0.5)
+    names = sorted(set(opts) | {"pace_kb"})
+    old = {k: _lib.get_option(k) for k in names}
+    try:
+        _lib.set_option("pace_kb", 0)
+        base = run_cuda(inp, "bf16")
+        for k, v in opts.items():
+            _lib.set_option(k, v)
+        got = run_cuda(inp, "bf16")
+        assert _lib.device_status() == 0
+        if "pace_limit_us" not in opts:
+            # every CTA was resident and on time: pacing was not switched off
+            assert _lib.get_option("pace_off") == 0
+    finally:
+        for k, v in old.items():
+            _lib.set_option(k, v)
+    for k in base:
+        assert np.array_equal(got[k], base[k]), (opts, k)
+
+
 # ------------------------------------------------------------- fp16 paths --
 @pytest.mark.parametrize("d_model", [1024, 2048])
 def test_fp16_fast_accum_against_fp32_accum(d_model):
