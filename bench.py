@@ -50,9 +50,9 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 # for the kernel named, on the workload named; see profiles/.  None = not captured.
 NCU_TRAFFIC_BYTES = {
     # profiles/dram_traffic_llama3_8b_mlp.md (one launch each, full-size workload)
-    ("fwd_dual_gemm", "llama3_8b_mlp", 1): 5.94e9 + 2.79e9,
-    ("dx_gemm", "llama3_8b_mlp", 1): 9.58e9 + 0.26e9,
-    ("dw_dual_gemm", "llama3_8b_mlp", 1): 9.18e9 + 0.24e9,
+    ("fwd_dual_gemm", "llama3_8b_mlp", 1): 4.52e9 + 2.79e9,
+    ("dx_gemm", "llama3_8b_mlp", 1): 5.52e9 + 0.26e9,
+    ("dw_dual_gemm", "llama3_8b_mlp", 1): 5.60e9 + 0.24e9,
     ("gate_grad_elementwise", "llama3_8b_mlp", 1): 2.82e9 + 1.82e9,
 }
 
