@@ -186,10 +186,13 @@ static int ensure_device(DeviceInfo** out) {
 // ------------------------------------------------------------- tensor maps --
 // Row-major (outer, inner) array of 16-bit elements; box = box_outer rows of 64
 // elements (128 bytes, 128-byte swizzle) or of 32 elements (64 bytes, 64-byte swizzle).
+// `row_elems` is the distance between rows in elements when the map covers a column
+// range of a wider array (0 = dense, rows are `inner` elements apart).
 static int make_map(CUtensorMap* m, const void* ptr, int dtype, uint64_t inner, uint64_t outer,
-                    uint32_t box_outer, const char* what, uint32_t box_inner = 64) {
+                    uint32_t box_outer, const char* what, uint32_t box_inner = 64,
+                    uint64_t row_elems = 0) {
   cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {inner * 2};
+  cuuint64_t strides[1] = {(row_elems ? row_elems : inner) * 2};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode(
@@ -342,6 +345,7 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   const int tile_n = ((MODE == MODE_FWD || MODE == MODE_DW) ? 128 : 256) * nsub;
   p.num_m_tiles = (rows + tile_m - 1) / tile_m;
   p.num_n_tiles = (p.N + tile_n - 1) / tile_n;
+  if (p.ldc == 0) p.ldc = p.N;
   p.status = d->status;
   p.clk_probe = d->clk_probe;
   p.l2_a = (int)g_opt.l2_a;
@@ -773,20 +777,29 @@ int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const vo
                            static_cast<cudaStream_t>(stream), d, tc);
 }
 
-int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate, void* dw_up,
-                    int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream) {
+// Columns [col0, col0 + ncols) of both weight gradients; all pointers are to the
+// full arrays, whose rows are di elements long.
+static int backward_dw_columns(const void* x, const void* dg, const void* du, void* dw_gate,
+                               void* dw_up, int64_t T, int64_t dm, int64_t di, int64_t col0,
+                               int64_t ncols, int dtype, int accum, void* stream) {
   int rc = check_common(T, dm, di, dtype, accum);
   if (rc != FSW_OK) return rc;
+  if (col0 < 0 || ncols < 0 || col0 + ncols > di || (col0 % 8) != 0 || (ncols % 8) != 0)
+    return fail(FSW_EINVAL, "column range [%lld, +%lld) must lie in [0, %lld) and be multiples of 8",
+                (long long)col0, (long long)ncols, (long long)di);
   if (!dw_gate || !dw_up) return fail(FSW_EINVAL, "NULL pointer");
   if (!aligned16(x) || !aligned16(dg) || !aligned16(du) || !aligned16(dw_gate) || !aligned16(dw_up))
     return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
   DeviceInfo* d = nullptr;
   if ((rc = ensure_device(&d)) != FSW_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (ncols == 0) return FSW_OK;
+  char* wg_out = static_cast<char*>(dw_gate) + col0 * 2;
+  char* wu_out = static_cast<char*>(dw_up) + col0 * 2;
   if (T == 0) {
     // An empty reduction: the gradients are exactly zero.
-    FSW_CUDA(cudaMemsetAsync(dw_gate, 0, (size_t)dm * di * 2, st));
-    FSW_CUDA(cudaMemsetAsync(dw_up, 0, (size_t)dm * di * 2, st));
+    FSW_CUDA(cudaMemset2DAsync(wg_out, (size_t)di * 2, 0, (size_t)ncols * 2, (size_t)dm, st));
+    FSW_CUDA(cudaMemset2DAsync(wu_out, (size_t)di * 2, 0, (size_t)ncols * 2, (size_t)dm, st));
     return FSW_OK;
   }
   if (!x || !dg || !du) return fail(FSW_EINVAL, "NULL pointer");
@@ -794,15 +807,31 @@ int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate
   memset(&p, 0, sizeof(p));
   if ((rc = make_map(&p.a0, x, dtype, dm, T, 64, "x^T")) != FSW_OK) return rc;
   p.a1 = p.a0;
-  if ((rc = make_map(&p.b0, dg, dtype, di, T, 64, "dg")) != FSW_OK) return rc;
-  if ((rc = make_map(&p.b1, du, dtype, di, T, 64, "du")) != FSW_OK) return rc;
-  p.c0_ptr = dw_gate;
-  p.c1_ptr = dw_up;
+  if ((rc = make_map(&p.b0, static_cast<const char*>(dg) + col0 * 2, dtype, ncols, T, 64, "dg", 64,
+                     di)) != FSW_OK)
+    return rc;
+  if ((rc = make_map(&p.b1, static_cast<const char*>(du) + col0 * 2, dtype, ncols, T, 64, "du", 64,
+                     di)) != FSW_OK)
+    return rc;
+  p.c0_ptr = wg_out;
+  p.c1_ptr = wu_out;
   p.M = (int)dm;
-  p.N = (int)di;
+  p.N = (int)ncols;
+  p.ldc = (int)di;
   p.num_k_blocks = (int)((T + 63) / 64);
   return run_gemm<MODE_DW>(p, (int)dm, dtype, accum == FSW_ACC_F16, st, d,
-                           choose_tiles(MODE_DW, dm, di, d));
+                           choose_tiles(MODE_DW, dm, ncols, d));
+}
+
+int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate, void* dw_up,
+                    int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream) {
+  return backward_dw_columns(x, dg, du, dw_gate, dw_up, T, dm, di, 0, di, dtype, accum, stream);
+}
+
+int fsw_backward_dw_columns(const void* x, const void* dg, const void* du, void* dw_gate,
+                            void* dw_up, int64_t T, int64_t dm, int64_t di, int64_t col0,
+                            int64_t ncols, int dtype, int accum, void* stream) {
+  return backward_dw_columns(x, dg, du, dw_gate, dw_up, T, dm, di, col0, ncols, dtype, accum, stream);
 }
 
 int fsw_backward(const void* dout, const void* x, const void* w_gate, const void* w_up,

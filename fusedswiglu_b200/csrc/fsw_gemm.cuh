@@ -69,6 +69,7 @@ struct GemmParams {
   uint32_t a_kadv, b_kadv; // bytes to advance the start address per K=16 step
   uint32_t idesc;          // UMMA instruction descriptor
   int M, N;                // output extents: rows, columns (per output tensor)
+  int ldc;                 // elements between output rows (N unless a column range is written)
   int num_m_tiles, num_n_tiles, group_m;
   int num_k_blocks;        // 64-wide K blocks per product
   int store_gu;            // MODE_FWD: also write g and u
@@ -316,7 +317,7 @@ __device__ __forceinline__ void stage_rows128(uint32_t buf, int lane, const uint
     ptx::st_shared_v4(base + ((c ^ x) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
 }
 __device__ __forceinline__ void flush_rows128(uint32_t buf, int lane, void* out, int row0, int col0,
-                                              int M, int N) {
+                                              int M, int N, int ld) {
   const int c = lane & 7;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -325,7 +326,7 @@ __device__ __forceinline__ void flush_rows128(uint32_t buf, int lane, void* out,
     ptx::ld_shared_v4(buf + r * 128u + ((c ^ (r & 7)) << 4), a, b, cc, d);
     const int row = row0 + r, col = col0 + c * 8;
     if (row < M && col < N)
-      ptx::st_global_v4(static_cast<char*>(out) + (static_cast<size_t>(row) * N + col) * 2, a, b, cc,
+      ptx::st_global_v4(static_cast<char*>(out) + (static_cast<size_t>(row) * ld + col) * 2, a, b, cc,
                         d);
   }
 }
@@ -480,7 +481,7 @@ __device__ __forceinline__ void drain_plain(const GemmParams& p, const EpiCtx& e
     void* out = (MODE == MODE_DW && jb >= 2) ? p.c1_ptr : p.c0_ptr;
     stage_rows128(e.buf, e.lane, pk);
     __syncwarp();
-    flush_rows128(e.buf, e.lane, out, e.row0, col, p.M, p.N);
+    flush_rows128(e.buf, e.lane, out, e.row0, col, p.M, p.N, p.ldc);
     __syncwarp();
   }
 }

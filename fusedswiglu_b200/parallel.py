@@ -41,6 +41,39 @@ def comm_sms(world_size: int) -> int:
     return 16 if world_size <= 2 else 32
 
 
+# Planning figures for the part of the dW GEMM that runs beside the all-reduce of dX:
+# the bus bandwidth NCCL reaches through NVSwitch while confined to comm_sms() SMs beside a
+# GEMM (measured on 8xB200 from the exposed time of a 268 MB and a 1.07 GB all-reduce:
+# ~215 GB/s on 2 ranks, ~225 on 4, ~490 on 8, where the switch reduces), its fixed
+# cost, and the sustained rate of the GEMM on the full GPU.
+ALLREDUCE_BUS_BYTES_PER_S = {2: 215e9, 4: 225e9, 8: 490e9}
+ALLREDUCE_BUS_BYTES_PER_S_OTHER = 225e9
+ALLREDUCE_FIXED_S = 40e-6
+GEMM_SUSTAINED_FLOPS = 1.35e15
+DW_SPLIT_ALIGN = 256  # columns per dW tile
+
+
+def plan_dw_split(T: int, dm: int, di_local: int, world_size: int, sm_count: int, reserve: int,
+                  elem_bytes: int = 2) -> int:
+    """Columns of the local dW GEMM to run on ``sm_count - reserve`` SMs beside the
+    all-reduce of dX (T x dm elements); the remaining columns run afterwards on all
+    SMs.  The first part is sized to last 1.1x the estimated all-reduce time; returns
+    ``di_local`` when the whole GEMM is needed to cover it."""
+    if world_size <= 1 or reserve <= 0:
+        return 0
+    bus = ALLREDUCE_BUS_BYTES_PER_S.get(world_size, ALLREDUCE_BUS_BYTES_PER_S_OTHER)
+    t_ar = 2.0 * (world_size - 1) / world_size * T * dm * elem_bytes / bus
+    t_ar += ALLREDUCE_FIXED_S
+    rate = GEMM_SUSTAINED_FLOPS * max(1, sm_count - reserve) / sm_count
+    t_dw = 4.0 * T * dm * di_local / rate
+    cols = int(di_local * min(1.0, 1.1 * t_ar / t_dw))
+    cols = -(-cols // DW_SPLIT_ALIGN) * DW_SPLIT_ALIGN
+    # a tail of less than two tiles is not worth a launch of its own
+    if cols + 2 * DW_SPLIT_ALIGN > di_local:
+        return di_local
+    return cols
+
+
 def shard_bounds(d_intermediate: int, rank: int, world_size: int) -> Tuple[int, int]:
     """Column range of `rank`; d_intermediate must split into equal 8-aligned parts."""
     if world_size < 1 or not (0 <= rank < world_size):
@@ -79,17 +112,31 @@ class _CudaBackend:
     gemm = staticmethod(_launch.gemm)
 
     @staticmethod
-    def grad_weights_beside_collective(x2d, dg, du, *, fast_accum=False, world_size=2):
-        """dW GEMM on all but comm_sms(world_size) SMs, so a concurrent collective can run."""
+    def grad_weights_beside_collective(x2d, dg, du, *, fast_accum=False, world_size=2, work=None):
+        """dW GEMM while the all-reduce of dX (``work``) is in flight.
+
+        NCCL's kernel makes no progress until all of its CTAs are resident, so the
+        columns of dW that overlap it run on all but comm_sms(world_size) SMs.  When
+        the GEMM is longer than the collective, only a first column range sized to
+        the collective's estimated duration runs that way; the current stream then
+        waits for the collective and the remaining columns get the whole GPU."""
         reserve = comm_sms(world_size)
         if reserve <= 0:
             return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum)
         sms = _lib.get_option("sm_count")
+        T, dm = x2d.shape
+        di = dg.shape[1]
+        first = plan_dw_split(T, dm, di, world_size, sms, reserve, x2d.element_size()) if work is not None else di
         _lib.set_option("gemm_max_sms", max(2, sms - reserve))
         try:
-            return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum)
+            if first >= di:
+                return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum)
+            dwg, dwu = _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum, columns=(0, first))
         finally:
             _lib.set_option("gemm_max_sms", 0)
+        work.wait()  # stream-level: the rest starts when the collective's kernel has left the SMs
+        return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum, out_gate=dwg, out_up=dwu,
+                                    columns=(first, di - first))
 
 
 class ColumnParallelSwiGLU(Function):
@@ -126,7 +173,7 @@ class ColumnParallelSwiGLU(Function):
             work = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group, async_op=True)
         if work is not None and hasattr(backend, "grad_weights_beside_collective"):
             dwg, dwu = backend.grad_weights_beside_collective(
-                x2d, dg, du, fast_accum=fast_accum, world_size=dist.get_world_size(group))
+                x2d, dg, du, fast_accum=fast_accum, world_size=dist.get_world_size(group), work=work)
         else:
             dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=fast_accum)
         if work is not None:
@@ -184,7 +231,7 @@ class TensorParallelSwiGLUMLP(Function):
             work = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group, async_op=True)
         if work is not None and hasattr(backend, "grad_weights_beside_collective"):
             dwg, dwu = backend.grad_weights_beside_collective(
-                x2d, dg, du, fast_accum=False, world_size=dist.get_world_size(group))
+                x2d, dg, du, fast_accum=False, world_size=dist.get_world_size(group), work=work)
         else:
             dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=False)
         if work is not None:

@@ -76,6 +76,19 @@ int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate
                     int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream);
 
 /*
+ * fsw_backward_dw restricted to columns [col0, col0 + ncols) of dw_gate and dw_up
+ * (col0 and ncols multiples of 8).  All pointers are to the FULL arrays: dg and du
+ * (T, di), dw_gate and dw_up (dm, di); only the named columns are read and written,
+ * and they get exactly the values fsw_backward_dw would give them.  Lets a caller cut
+ * the weight-gradient GEMM into pieces, e.g. to run one piece beside a collective on
+ * fewer SMs ("gemm_max_sms") and the rest on the whole GPU.  No counterpart in the
+ * reference, whose fused_bmm always covers all of d_intermediate.
+ */
+int fsw_backward_dw_columns(const void* x, const void* dg, const void* du, void* dw_gate,
+                            void* dw_up, int64_t T, int64_t dm, int64_t di, int64_t col0,
+                            int64_t ncols, int dtype, int accum, void* stream);
+
+/*
  * Whole backward on one stream: elementwise step into the caller's scratch
  * (`dg_scratch`, `du_scratch`, each T*di elements), then dx, then dw.
  * Replaces FusedSwiGLU.backward (fused_swiglu/swiglu.py:34-58).

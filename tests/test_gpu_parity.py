@@ -248,6 +248,54 @@ def test_producer_pacing_does_not_change_results(opts):
         assert np.array_equal(got[k], base[k]), (opts, k)
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+def test_weight_gradient_column_ranges_equal_the_full_gemm(dtype):
+    """fsw_backward_dw_columns writes exactly the values of fsw_backward_dw into the
+    named columns and nothing anywhere else, for ragged ranges too."""
+    from fusedswiglu_b200 import _launch
+
+    T, dm, di = 1000, 320, 1096
+    inp = orc.make_inputs(1, T, dm, di, dtype, seed=5, dout_std=0.5)
+    x = dev(inp["x"].reshape(T, dm), dtype)
+    dg = dev(inp["dout"].reshape(T, di), dtype)
+    du = dev((inp["dout"] * 0.5 + 0.25).reshape(T, di), dtype)
+    full_g, full_u = _launch.grad_weights(x, dg, du)
+    for first, count in [(0, 256), (256, 840), (8, 16), (1088, 8), (0, di), (512, 0)]:
+        out_g = torch.full_like(full_g, 7.0)
+        out_u = torch.full_like(full_u, -3.0)
+        _launch.grad_weights(x, dg, du, out_gate=out_g, out_up=out_u, columns=(first, count))
+        torch.cuda.synchronize()
+        sl = slice(first, first + count)
+        assert torch.equal(out_g[:, sl], full_g[:, sl]) and torch.equal(out_u[:, sl], full_u[:, sl])
+        keep = torch.ones(di, dtype=torch.bool, device=out_g.device)
+        keep[sl] = False
+        assert bool((out_g[:, keep] == 7.0).all()) and bool((out_u[:, keep] == -3.0).all())
+
+
+def test_dw_beside_a_collective_in_two_parts_equals_one_launch(monkeypatch):
+    """The split the column-parallel backward uses when the dW GEMM outlasts the
+    all-reduce: first columns on fewer SMs, wait for the collective, rest on all SMs."""
+    from fusedswiglu_b200 import _launch, _lib, parallel
+
+    class Done:
+        waited = 0
+
+        def wait(self):
+            Done.waited += 1
+
+    T, dm, di = 2048, 512, 1536
+    inp = orc.make_inputs(1, T, dm, di, "bf16", seed=6, dout_std=0.5)
+    x = dev(inp["x"].reshape(T, dm), "bf16")
+    dg = dev(inp["dout"].reshape(T, di), "bf16")
+    du = dev((inp["dout"] * 0.5).reshape(T, di), "bf16")
+    want_g, want_u = _launch.grad_weights(x, dg, du)
+    monkeypatch.setattr(parallel, "plan_dw_split", lambda *a, **k: 512)
+    got_g, got_u = parallel._CudaBackend.grad_weights_beside_collective(x, dg, du, world_size=4, work=Done())
+    torch.cuda.synchronize()
+    assert Done.waited == 1 and _lib.get_option("gemm_max_sms") == 0
+    assert torch.equal(got_g, want_g) and torch.equal(got_u, want_u)
+
+
 # ------------------------------------------------------------- fp16 paths --
 @pytest.mark.parametrize("d_model", [1024, 2048])
 def test_fp16_fast_accum_against_fp32_accum(d_model):

@@ -208,6 +208,26 @@ def _absent_rank_worker(rank, world, port, q):
             pass
 
 
+def test_plan_of_the_dw_split_beside_the_all_reduce():
+    """The column count that runs beside the collective is a whole number of tiles,
+    grows with the collective's size relative to the GEMM, and covers the whole GEMM
+    when the collective is the longer of the two."""
+    from fusedswiglu_b200.parallel import plan_dw_split, DW_SPLIT_ALIGN
+
+    assert plan_dw_split(32768, 4096, 14336, 1, 148, 16) == 0          # no collective
+    assert plan_dw_split(32768, 4096, 7168, 2, 148, 0) == 0            # nothing reserved
+    for T, dm, di, world, reserve in [(32768, 4096, 7168, 2, 16), (65536, 8192, 7168, 4, 32),
+                                      (65536, 8192, 14336, 2, 16)]:
+        c = plan_dw_split(T, dm, di, world, 148, reserve)
+        assert 0 < c < di and c % DW_SPLIT_ALIGN == 0, (T, dm, di, world, c)
+    # 8 ranks: the local GEMM is shorter than the all-reduce of the full dX
+    assert plan_dw_split(32768, 4096, 1792, 8, 148, 32) == 1792
+    # tiny problems are dominated by the collective's fixed cost
+    assert plan_dw_split(128, 512, 768, 2, 148, 16) == 768
+    # more ranks -> more bytes per rank on the wire -> a larger first part
+    assert plan_dw_split(65536, 8192, 7168, 8, 148, 32) >= plan_dw_split(65536, 8192, 7168, 2, 148, 32)
+
+
 def test_rank_that_never_joins_ends_the_collective_with_an_error():
     world = 2
     ctx = mp.get_context("spawn")
