@@ -167,12 +167,17 @@ int64_t fsw_status(void);
 /*
  * Tuning and debugging knobs, process-wide.  Main names: "cta_group" (1 or 2 CTAs
  * per MMA, 0 = automatic), "nsub" (1 or 2 accumulator regions per tile, 0 =
- * automatic), "group_m" (tile
- * rasterisation group height in tiles, 0 = automatic), "gemm_max_sms" (cap on the
- * SMs a GEMM launch occupies, 0 = all; used to leave room for a concurrent
- * collective), "ew_blocks_per_sm".  Read-only facts through fsw_get_option:
- * "sm_count", "max_pairs", "stages", "last_sm_khz".  Returns FSW_EINVAL for an
- * unknown name or value.  fsw_get_option returns the current value or -1.
+ * automatic), "group_m" (tile rasterisation group height in tiles, 0 = automatic),
+ * "gemm_max_sms" (cap on the SMs a GEMM launch occupies, 0 = all; used to leave room
+ * for a concurrent collective), "pace_kb" (the TMA producers of all CTAs of a GEMM
+ * meet every pace_kb K blocks so that both dies of the GPU stream the same operand
+ * panels at the same time and share them in L2; 0 = free-running; advisory, never
+ * changes results), "pace_limit_us" (longest wait at one meeting), "l2_a", "l2_b",
+ * "l2_out" (L2 eviction priority of operand loads and forward stores: 0 normal,
+ * 1 evict first, 2 evict last), "ew_blocks_per_sm".  Read-only facts through
+ * fsw_get_option: "sm_count", "max_pairs", "stages", "last_sm_khz", "pace_off" (1 if
+ * the last paced launch gave its pacing up).  Returns FSW_EINVAL for an unknown name
+ * or value.  fsw_get_option returns the current value or -1.
  */
 int fsw_set_option(const char* name, int64_t value);
 int64_t fsw_get_option(const char* name);
