@@ -228,6 +228,62 @@ def test_plan_of_the_dw_split_beside_the_all_reduce():
     assert plan_dw_split(65536, 8192, 14336, 2, 148, 16) / 14336 < plan_dw_split(65536, 8192, 7168, 2, 148, 16) / 7168
 
 
+def test_dw_beside_collective_call_sequence(monkeypatch):
+    """Host logic of the dW launch beside the all-reduce, with the library and the
+    launchers replaced by recorders (no GPU): SMs are reserved only for the first
+    column range, the stream waits for the collective before the rest, and the
+    reservation is lifted even if a launch raises."""
+    import torch
+    from fusedswiglu_b200 import parallel
+
+    log = []
+    opts = {"sm_count": 148, "gemm_max_sms": 0}
+
+    class FakeLib:
+        @staticmethod
+        def get_option(name):
+            return opts[name]
+
+        @staticmethod
+        def set_option(name, value):
+            opts[name] = value
+            log.append(("set", name, value))
+
+    class FakeLaunch:
+        fail = False
+
+        @staticmethod
+        def grad_weights(x2d, dg, du, *, fast_accum=False, out_gate=None, out_up=None, columns=None):
+            if FakeLaunch.fail:
+                raise RuntimeError("launch failed")
+            log.append(("dw", columns, opts["gemm_max_sms"], out_gate is not None))
+            return (out_gate if out_gate is not None else "dwg"), (out_up if out_up is not None else "dwu")
+
+    class Work:
+        def wait(self):
+            log.append(("wait",))
+
+    monkeypatch.setattr(parallel, "_lib", FakeLib)
+    monkeypatch.setattr(parallel, "_launch", FakeLaunch)
+    x2d, dg = torch.empty(65536, 8192, device="meta", dtype=torch.bfloat16), torch.empty(65536, 7168, device="meta", dtype=torch.bfloat16)
+    first = parallel.plan_dw_split(65536, 8192, 7168, 4, 148, 32)
+    out = parallel._CudaBackend.grad_weights_beside_collective(x2d, dg, dg, world_size=4, work=Work())
+    assert out == ("dwg", "dwu")
+    assert log == [("set", "gemm_max_sms", 116), ("dw", (0, first), 116, False), ("set", "gemm_max_sms", 0),
+                   ("wait",), ("dw", (first, 7168 - first), 0, True)]
+    # the collective outlasts the GEMM (8 ranks, 8B shape): one launch, all of it on the reduced SM count
+    log.clear()
+    x2d, dg = torch.empty(32768, 4096, device="meta", dtype=torch.bfloat16), torch.empty(32768, 1792, device="meta", dtype=torch.bfloat16)
+    parallel._CudaBackend.grad_weights_beside_collective(x2d, dg, dg, world_size=8, work=Work())
+    assert log == [("set", "gemm_max_sms", 116), ("dw", None, 116, False), ("set", "gemm_max_sms", 0)]
+    # a failing launch still lifts the reservation
+    log.clear()
+    FakeLaunch.fail = True
+    with pytest.raises(RuntimeError):
+        parallel._CudaBackend.grad_weights_beside_collective(x2d, dg, dg, world_size=8, work=Work())
+    assert opts["gemm_max_sms"] == 0
+
+
 def test_rank_that_never_joins_ends_the_collective_with_an_error():
     world = 2
     ctx = mp.get_context("spawn")
