@@ -5,17 +5,21 @@
 
 One "step" is one forward + backward pass of the SwiGLU MLP block over one batch
 of seeded synthetic tensors: the forward dual GEMM, the gate-gradient elementwise
-kernel, the dX GEMM and the dW dual GEMM (4 kernel launches of this library).
-FLOPs are counted as 2*M*N*K per GEMM, six GEMMs: 12*T*d_model*d_intermediate per
-step; elementwise work is not counted.
+kernel, the dX GEMM and the dW dual GEMM.  FLOPs are counted as 2*M*N*K per GEMM,
+six GEMMs: 12*T*d_model*d_intermediate per step; elementwise work is not counted.
 
 With N > 1 (launched by torch.distributed.run, one rank per GPU) d_intermediate is
-sharded column-parallel: forward and dW are local, the partial dX is all-reduced
-with NCCL while the dW GEMM runs.  The total problem is fixed, so scaling is
-"strong".
+sharded column-parallel and the timed loop IS the package's multi-GPU API
+(ColumnParallelSwiGLU forward + backward): forward and dW are local, the partial
+dX is all-reduced with NCCL while the dW GEMM runs.  The total problem is fixed,
+so scaling is "strong".
+
+After the timed region (outside it) every run checks its own results, per tensor,
+against float64 on sampled rows and columns and puts the figures into the JSON line
+(`parity`); a relative error above 1e-2 fails the run.
 
 `--impl reference` times the reference path's PyTorch SwiGLU (forward + autograd
-backward) on the host CPU cores over a bounded sample of the same workload.
+backward) on the host CPU cores.
 """
 from __future__ import annotations
 
@@ -24,6 +28,7 @@ import json
 import os
 import subprocess
 import sys
+import threading
 import time
 from pathlib import Path
 
@@ -45,16 +50,10 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "llama3_8b_mlp"
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
-
-# DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum)
-# for the kernel named, on the workload named; see profiles/.  None = not captured.
-NCU_TRAFFIC_BYTES = {
-    # profiles/dram_traffic_llama3_8b_mlp.md (one launch each, full-size workload)
-    ("fwd_dual_gemm", "llama3_8b_mlp", 1): 4.52e9 + 2.79e9,
-    ("dx_gemm", "llama3_8b_mlp", 1): 5.52e9 + 0.26e9,
-    ("dw_dual_gemm", "llama3_8b_mlp", 1): 5.60e9 + 0.24e9,
-    ("gate_grad_elementwise", "llama3_8b_mlp", 1): 2.82e9 + 1.82e9,
-}
+PARITY_BOUND = 1e-2  # the reference's bound on ||a-b||_F/||b||_F (fused_swiglu/test_swiglu.py:20)
+# DRAM bytes per launch from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum),
+# keyed "kernel/workload/n_gpus"; absent = not captured for that case.
+DRAM_TRAFFIC_FILE = REPO / "profiles" / "dram_traffic_per_launch.json"
 
 CLOCK_QUERY = (
     "timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -70,8 +69,12 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--preheat", type=float, default=1.0, metavar="SECONDS",
+                    help="run the same step loop for this long before the warm-up steps, so that short timed "
+                         "regions (many GPUs) are measured at the power-capped clock like long ones")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-gpu-bar", action="store_true",
                     help="skip timing torch's own CUDA SwiGLU (cuBLAS + eager kernels) on the same GPU")
     ap.add_argument("--seed", type=int, default=0)
@@ -97,69 +100,120 @@ def load_peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+def load_dram_traffic(kernel, workload, world):
+    try:
+        return json.loads(DRAM_TRAFFIC_FILE.read_text()).get(f"{kernel}/{workload}/{world}")
+    except Exception:
+        return None
 
-    def __init__(self, gpu_id: str):
-        self.gpu_id = gpu_id
-        self.proc = None
-        self.path = None
+
+def host_threads():
+    """Host threads this process may use (torch.distributed.run exports
+    OMP_NUM_THREADS=1, which must not decide the CPU baseline's thread count)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+# ------------------------------------------------------------ clock sampling --
+REASON_BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
+
+
+class ClockSampler:
+    """Samples SM clock, power and clock-event reasons while a region runs: NVML
+    polled from a thread every few milliseconds (read-only queries, the ones
+    nvidia-smi makes), or, if NVML cannot be loaded, an nvidia-smi loop."""
+
+    def __init__(self, gpu_uuid: str, index: int):
+        self.uuid, self.index = gpu_uuid, index
+        self.rows = []  # (host time, sm MHz, power W, reasons bitmask)
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._smi = None
+        self._smi_path = None
+        self.source = None
 
     def start(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            try:
+                h = pynvml.nvmlDeviceGetHandleByUUID(self.uuid.encode() if isinstance(self.uuid, str) else self.uuid)
+            except Exception:
+                h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        self.rows.append((time.time(), float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)),
+                                          pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0,
+                                          int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))))
+                    except Exception:
+                        pass
+                    time.sleep(0.004)
+
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+            self.source = "nvml, 4 ms period"
+            return
+        except Exception:
+            self._thread = None
         import tempfile
 
-        fd, self.path = tempfile.mkstemp(prefix="fsw_clocks_", suffix=".csv")
+        fd, self._smi_path = tempfile.mkstemp(prefix="fsw_clocks_", suffix=".csv")
         os.close(fd)
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
-                 "-i", self.gpu_id],
-                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL,
-            )
+            self._smi = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
+                 "-i", self.uuid or str(self.index)],
+                stdout=open(self._smi_path, "w"), stderr=subprocess.DEVNULL)
+            self.source = "nvidia-smi -lms 20"
         except OSError:
-            self.proc = None
+            self._smi = None
 
-    def stop(self, t_begin=None, t_end=None):
-        """Summarise the samples; with a (t_begin, t_end) host-time window only the
-        samples taken inside it count (falling back to all if none did)."""
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        rows = []
-        for line in Path(self.path).read_text().splitlines():
-            f = [s.strip() for s in line.split(",")]
-            if len(f) >= 9:
-                rows.append(f)
-        os.unlink(self.path)
-        if t_begin is not None and t_end is not None:
+    def _finish(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+            self._thread = None
+        if self._smi is not None:
             import datetime
 
-            inside = []
-            for r in rows:
+            self._smi.terminate()
+            try:
+                self._smi.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._smi.kill()
+            self._smi = None
+            for line in Path(self._smi_path).read_text().splitlines():
+                f = [s.strip() for s in line.split(",")]
+                if len(f) < 9:
+                    continue
                 try:
-                    ts = datetime.datetime.strptime(r[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    mask = sum(bit for i, (_, bit) in enumerate(REASON_BITS) if f[5 + i].lower().startswith("active"))
+                    self.rows.append((ts, float(f[1]), float(f[3]), mask))
+                    self.max_mhz = float(f[2])
                 except ValueError:
                     continue
-                if t_begin <= ts <= t_end:
-                    inside.append(r)
-            if inside:
-                rows = inside
-                out["window"] = "timed region"
-            else:
-                out["window"] = "warm-up and timed region (no sample fell inside the timed region)"
-        if not rows:
-            return out
-        sm = sorted(float(r[1]) for r in rows if r[1].replace(".", "").isdigit())
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[5 + i].lower().startswith("active") for r in rows)]
-        out.update(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=float(rows[0][2]) if rows[0][2] else None,
-                   reasons=reasons, samples=len(rows),
-                   power_w_max=max((float(r[3]) for r in rows if r[3].replace(".", "").isdigit()), default=None))
+            os.unlink(self._smi_path)
+
+    def summary(self, t_begin, t_end, label):
+        """Median SM clock and the reasons seen among the samples taken in [t_begin, t_end]."""
+        self._finish()
+        rows = [r for r in self.rows if t_begin <= r[0] <= t_end]
+        out = {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": len(rows), "window": label,
+               "source": self.source}
+        if rows:
+            sm = sorted(r[1] for r in rows)
+            out.update(sm_mhz=sm[len(sm) // 2], sm_mhz_min=sm[0], sm_mhz_max=sm[-1],
+                       reasons=[n for n, bit in REASON_BITS if any(r[3] & bit for r in rows)],
+                       power_w_max=max(r[2] for r in rows))
         return out
 
 
@@ -168,13 +222,24 @@ def flops_per_step(T, dm, di):
 
 
 # ------------------------------------------------------------ reference arm --
+def cpu_sample_tokens(T, dm, di):
+    """Tokens per CPU step: the whole workload when that is at most ~25 TFLOP of
+    work (a few seconds on a host of this class), else the largest T/2^k that is."""
+    t = T
+    while flops_per_step(t, dm, di) > 25e12 and t % 2 == 0 and t > 1024:
+        t //= 2
+    return t
+
+
 def cpu_reference_run(bs, sq, dm, di, dtype, steps, warmup, sample_tokens, seed=0):
-    """The reference path's PyTorch SwiGLU + autograd on the host cores, over
-    `sample_tokens` tokens of the workload per step."""
+    """The reference path's PyTorch SwiGLU + autograd (fused_swiglu/test_swiglu.py:47-55,
+    96-103) on the host cores, over `sample_tokens` tokens of the workload per step."""
     import torch
 
     from oracle import swiglu_oracle as orc
 
+    threads = host_threads()
+    torch.set_num_threads(threads)
     tdt = {"bf16": torch.bfloat16, "fp16": torch.float16}[dtype]
     T = min(sample_tokens, bs * sq)
     g = torch.Generator().manual_seed(seed)
@@ -198,16 +263,29 @@ def cpu_reference_run(bs, sq, dm, di, dtype, steps, warmup, sample_tokens, seed=
             "threads": torch.get_num_threads()}
 
 
+def cpu_baseline_object(r, T, steps, warmup):
+    import torch
+
+    whole = r["tokens"] == T
+    return {"value": r["tflops"], "unit": "TFLOP/s", "cores": r["threads"], "kind": "port",
+            "sample": (f"the whole workload ({T} tokens) per step" if whole else
+                       f"{r['tokens']} of {T} tokens per step") +
+                      f", {steps} step(s) after {warmup} warm-up, {r['sec_per_step']:.2f} s per step; the reference's "
+                      f"PyTorch SwiGLU + autograd restated in oracle/ (the reference's own module needs its Triton "
+                      f"import chain and is not on this machine), torch {torch.__version__} CPU, "
+                      f"{r['threads']} threads of os.cpu_count()={os.cpu_count()}"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import torch
 
     bs, sq, dm, di, dtype = WORKLOADS[args.workload]
-    sample = 2048 if args.workload != "plumbing" else bs * sq
-    steps = max(1, min(args.steps, 5))
-    warmup = max(1, min(args.warmup, 1))
+    T = bs * sq
+    sample = cpu_sample_tokens(T, dm, di)
+    steps = max(1, min(args.steps, 3))
+    warmup = 1
     r = cpu_reference_run(bs, sq, dm, di, dtype, steps, warmup, sample, args.seed)
     line = {
         "impl": "reference",
@@ -216,13 +294,101 @@ def run_reference(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
         "config": {"workload": args.workload, "bs": bs, "sq": sq, "d_model": dm, "d_intermediate": di,
                    "sample_tokens_per_step": r["tokens"], "device": "host CPU"},
-        "cpu_baseline": {"value": r["tflops"], "unit": "TFLOP/s", "cores": r["threads"], "kind": "port",
-                         "sample": f"{r['tokens']} of {bs * sq} tokens per step, {steps} steps, torch "
-                                   f"{torch.__version__} CPU, os.cpu_count()={os.cpu_count()}"},
+        "cpu_baseline": cpu_baseline_object(r, T, steps, warmup),
         "e2e": {"value": r["tflops"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "fwd_tokens_per_s": None,
     }
     print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------- parity --
+class _Err:
+    """Running error figures of one tensor over several sampled blocks."""
+
+    def __init__(self):
+        self.num = self.den = 0.0
+        self.max_abs = self.max_rel = self.ref_max = 0.0
+        self.pending = []
+
+    def add(self, got, ref):
+        d = (got.double() - ref).abs()
+        self.num += float((d * d).sum())
+        self.den += float((ref * ref).sum())
+        self.max_abs = max(self.max_abs, float(d.max()))
+        self.ref_max = max(self.ref_max, float(ref.abs().max()))
+        self.pending.append((d, ref.abs()))
+
+    def reduce(self, dist, world, dev):
+        import torch
+
+        if world > 1:
+            t = torch.tensor([self.num, self.den], device=dev, dtype=torch.float64)
+            dist.all_reduce(t)
+            self.num, self.den = float(t[0]), float(t[1])
+            m = torch.tensor([self.max_abs, self.ref_max], device=dev, dtype=torch.float64)
+            dist.all_reduce(m, op=dist.ReduceOp.MAX)
+            self.max_abs, self.ref_max = float(m[0]), float(m[1])
+        # max-rel with max(|ref|, 1e-6 * max|ref|) as denominator (near-zero entries dominate it)
+        floor = 1e-6 * self.ref_max
+        for d, r in self.pending:
+            self.max_rel = max(self.max_rel, float((d / r.clamp_min(floor)).max())) if floor > 0 else self.max_rel
+        if world > 1:
+            m = torch.tensor([self.max_rel], device=dev, dtype=torch.float64)
+            dist.all_reduce(m, op=dist.ReduceOp.MAX)
+            self.max_rel = float(m[0])
+        self.pending = []
+        return {"rel_fro": (self.num / self.den) ** 0.5 if self.den > 0 else 0.0, "max_abs": self.max_abs,
+                "max_rel": self.max_rel}
+
+
+def parity_report(x2d, wg, wu, dout2d, out, dx, dwg, dwu, world, seed=1234, n_rows=64, n_cols=32):
+    """Per-tensor error of this run's results against float64 on sampled rows (out,
+    dX) and sampled columns (dW_gate, dW_up).  Collective: with world > 1 every rank
+    calls it; out and dW are checked on each rank's own columns, dX (all-reduced, the
+    same on every rank) against the float64 sum of the ranks' partial products."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    dev = x2d.device
+    T, dm = x2d.shape
+    di_local = wg.shape[1]
+    gen = torch.Generator().manual_seed(seed)  # CPU generator: the same rows on every rank
+    rows = torch.randperm(T, generator=gen)[:min(n_rows, T)].to(dev)
+    cols = torch.randperm(di_local, generator=gen)[:min(n_cols, di_local)].to(dev)
+    wg64, wu64 = wg.double(), wu.double()
+    errs = {k: _Err() for k in ("out", "dx", "dw_gate", "dw_up")}
+
+    xr = x2d[rows].double()
+    g, u = xr @ wg64, xr @ wu64
+    errs["out"].add(out[rows], F.silu(g) * u)
+    s = torch.sigmoid(g)
+    d = dout2d[rows].double()
+    dg, du = d * u * (s + g * s * (1 - s)), d * g * s
+    dx_ref = dg @ wg64.T + du @ wu64.T
+    if world > 1:
+        dist.all_reduce(dx_ref)
+    errs["dx"].add(dx[rows], dx_ref)
+    del wg64, wu64, g, u, s, d, dg, du
+
+    wgc, wuc = wg[:, cols].double(), wu[:, cols].double()
+    acc_g = torch.zeros(dm, cols.numel(), device=dev, dtype=torch.float64)
+    acc_u = torch.zeros_like(acc_g)
+    for r0 in range(0, T, 4096):
+        xc = x2d[r0:r0 + 4096].double()
+        g, u = xc @ wgc, xc @ wuc
+        s = torch.sigmoid(g)
+        d = dout2d[r0:r0 + 4096][:, cols].double()
+        acc_g += xc.T @ (d * u * (s + g * s * (1 - s)))
+        acc_u += xc.T @ (d * g * s)
+    errs["dw_gate"].add(dwg[:, cols], acc_g)
+    errs["dw_up"].add(dwu[:, cols], acc_u)
+    rep = {k: e.reduce(dist, world, dev) for k, e in errs.items()}
+    rep["reference"] = (f"float64 SwiGLU + gradient formulas on {rows.numel()} sampled rows (out, dX) and "
+                        f"{cols.numel()} sampled columns per rank (dW_gate, dW_up)")
+    rep["bound"] = PARITY_BOUND
+    rep["ok"] = all(rep[k]["rel_fro"] < PARITY_BOUND for k in errs)
+    return rep
 
 
 # ------------------------------------------------------------------ our arm --
@@ -272,34 +438,96 @@ def run_ours(args):
     wg = wg_full[:, lo:hi].contiguous()
     wu = wu_full[:, lo:hi].contiguous()
     del wg_full, wu_full
-    dout = torch.randn(bs, sq, di_local, device=dev, dtype=tdt, generator=g)
+    dout_full = torch.randn(bs, sq, di, device=dev, dtype=tdt, generator=g)
+    dout = dout_full[..., lo:hi].contiguous() if world > 1 or args.shard_of > 1 else dout_full
+    del dout_full
     if dtype == "fp16":
         dout *= 0.1  # the reference's dy = 0.1 * randn (test_swiglu.py:98)
     x2d = x.view(T, dm)
     dout2d = dout.view(T, di_local)
 
     names = ["fwd_dual_gemm", "gate_grad_elementwise", "dx_gemm", "dw_dual_gemm"]
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(K)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(K)]
+    launches = {"n": 0}
+    dw_split = {"first": None}
+
+    def counted(fn):
+        def wrapper(*a, **kw):
+            launches["n"] += 1
+            return fn(*a, **kw)
+        return wrapper
+
+    # Every C-ABI launch goes through these four functions; count them.
+    for _name in ("forward", "gate_grad", "grad_input", "grad_weights"):
+        setattr(_launch, _name, counted(getattr(_launch, _name)))
+
+    class Marked:
+        """The product backend with a CUDA event recorded before each launch."""
+        marks = None
+
+        @staticmethod
+        def _mark(i):
+            if Marked.marks is not None:
+                Marked.marks[i].record()
+
+        @staticmethod
+        def forward(*a, **kw):
+            Marked._mark(0)
+            return _launch.forward(*a, **kw)
+
+        @staticmethod
+        def gate_grad(*a, **kw):
+            Marked._mark(1)
+            return _launch.gate_grad(*a, **kw)
+
+        @staticmethod
+        def grad_input(*a, **kw):
+            Marked._mark(2)
+            return _launch.grad_input(*a, **kw)
+
+        @staticmethod
+        def grad_weights(*a, **kw):
+            Marked._mark(3)
+            r = _launch.grad_weights(*a, **kw)
+            Marked._mark(4)
+            return r
+
+        @staticmethod
+        def grad_weights_beside_collective(x2d_, dg, du, **kw):
+            Marked._mark(3)
+            if dw_split["first"] is None and kw.get("work") is not None:
+                dw_split["first"] = parallel.plan_dw_split(
+                    x2d_.shape[0], x2d_.shape[1], dg.shape[1], kw.get("world_size", world),
+                    _lib.get_option("sm_count"), parallel.comm_sms(world), x2d_.element_size(),
+                    kw.get("collective", "all_reduce"))
+            r = parallel._CudaBackend.grad_weights_beside_collective(x2d_, dg, du, **kw)
+            Marked._mark(4)
+            return r
+
+    wgp = wg.clone().requires_grad_(True)
+    wup = wu.clone().requires_grad_(True)
 
     def step(marks=None):
-        if marks: marks[0].record()
-        out, gg, uu = _launch.forward(x2d, wg, wu, fast_accum=fast)
-        if marks: marks[1].record()
-        dg, du = _launch.gate_grad(dout2d, gg, uu)
-        if marks: marks[2].record()
-        dx = _launch.grad_input(dg, du, wg, wu)
-        if marks: marks[3].record()
-        if world > 1:
-            work = dist.all_reduce(dx, async_op=True)
-            dwg, dwu = parallel._CudaBackend.grad_weights_beside_collective(
-                x2d, dg, du, fast_accum=fast, world_size=world)
-        else:
-            work = None
-            dwg, dwu = _launch.grad_weights(x2d, dg, du, fast_accum=fast)
-        if marks: marks[4].record()
-        if work is not None:
-            work.wait()
-        return out, dx, dwg, dwu
+        """One forward + backward.  world == 1: the launch sequence of FusedSwiGLU
+        (the autograd Function adds nothing on the device).  world > 1: the package's
+        ColumnParallelSwiGLU forward and backward themselves."""
+        if world == 1:
+            Marked.marks = marks
+            out, gg, uu = Marked.forward(x2d, wg, wu, fast_accum=fast)
+            dg, du = Marked.gate_grad(dout2d, gg, uu)
+            dx = Marked.grad_input(dg, du, wg, wu)
+            dwg, dwu = Marked.grad_weights(x2d, dg, du, fast_accum=fast)
+            if marks: marks[5].record()
+            Marked.marks = None
+            return out, dx, dwg, dwu
+        xin = x.detach().requires_grad_(True)
+        wgp.grad = wup.grad = None
+        Marked.marks = marks
+        out = parallel.column_parallel_swiglu(xin, wgp, wup, fast_accum=fast, backend=Marked)
+        out.backward(dout)
+        if marks: marks[5].record()
+        Marked.marks = None
+        return out.detach().view(T, di_local), xin.grad.view(T, dm), wgp.grad, wup.grad
 
     def barrier():
         if world > 1:
@@ -328,24 +556,38 @@ def run_ours(args):
         ms = t0.elapsed_time(t1) / K
         print(json.dumps({"only": args.only, "workload": args.workload, "ms": ms, "steps": K,
                           "tflops": (4.0 * T * dm * di_local / ms / 1e9) if args.only != "ew" else None,
+                          "sm_khz": _lib.get_option("last_sm_khz"),
                           "status": _lib.device_status()}), flush=True)
         return
 
-    # The clock sampler runs from the warm-up on (same workload), so that short
-    # timed regions still collect samples under load.
     props = torch.cuda.get_device_properties(dev)
-    gpu_id = str(getattr(props, "uuid", local_rank))
-    if not gpu_id.startswith("GPU-") and len(gpu_id) > 8:
+    gpu_id = str(getattr(props, "uuid", ""))
+    if gpu_id and not gpu_id.startswith("GPU-"):
         gpu_id = "GPU-" + gpu_id
-    sampler = ClockSampler(gpu_id if rank == 0 else str(local_rank))
+    sampler = ClockSampler(gpu_id, local_rank)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
+    # Pre-heat: the same step loop for a fixed wall time, so that the timed region of
+    # every GPU count starts at the clock the power cap settles at.
+    barrier()
+    pre0 = time.time()
+    pre_steps = 0
+    while True:
+        for _ in range(4):
+            step()
+            pre_steps += 1
+        torch.cuda.synchronize()
+        flag = torch.tensor([1.0 if time.time() - pre0 < args.preheat else 0.0], device=dev)
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)  # all ranks leave together
+        if float(flag.item()) == 0.0:
+            break
     for _ in range(W):
         step()
     barrier()
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    launches["n"] = 0
     wall0 = time.time()
     t_start.record()
     for i in range(K):
@@ -353,9 +595,15 @@ def run_ours(args):
     t_end.record()
     barrier()
     wall1 = time.time()
-    clocks = sampler.stop(wall0, wall1) if rank == 0 else None
+    n_launches = launches["n"]
+    clocks = None
+    if rank == 0:
+        clocks = sampler.summary(wall0, wall1, "timed region")
+        pre = ClockSampler.summary(sampler, pre0, wall0, "pre-heat and warm-up (same step loop)")
+        clocks["before_timed_region"] = {k: pre[k] for k in ("sm_mhz", "reasons", "samples", "window")}
     total_ms = t_start.elapsed_time(t_end)
     per_kernel_ms = [sum(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(K)) / K for j in range(4)]
+    tail_ms = sum(ev[i][4].elapsed_time(ev[i][5]) for i in range(K)) / K  # collective left exposed after dW
     if world > 1:
         tt = torch.tensor([total_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -368,23 +616,43 @@ def run_ours(args):
     total_flops = flops_per_step(T, dm, di)  # whole job, all ranks
     value = total_flops / ms_per_step / 1e9
 
+    # ---- parity of what the timed loop computed (outside the timed region)
+    parity = None
+    if not args.no_parity:
+        out_c, dx_c, dwg_c, dwu_c = step()
+        torch.cuda.synchronize()
+        parity = parity_report(x2d, wg, wu, dout2d, out_c, dx_c, dwg_c, dwu_c, world)
+        dx_keep_for_e2e = dx_c
+        del out_c, dwg_c, dwu_c
+        if not parity["ok"]:
+            if rank == 0:
+                print(json.dumps({"error": "parity check failed", "parity": parity}), flush=True)
+            raise SystemExit(f"results differ from float64 by more than {PARITY_BOUND}: {parity}")
+    else:
+        dx_keep_for_e2e = None
+
     # ---- end to end through the public autograd API with host buffers
     e2e = None
     if not args.no_e2e:
-        hx = torch.empty_like(x, device="cpu").pin_memory()
+        # world > 1: the tokens are sharded at the boundary as well (row_sharded mode):
+        # a rank uploads its T/world rows of x and its column shard of dout, and
+        # downloads the reduce-scattered dX of its own rows.
+        rs = world > 1 and bs % world == 0
+        b_mine = bs // world if rs else bs
+        x_src = x[rank * b_mine:(rank + 1) * b_mine] if rs else x
+        hx = torch.empty_like(x_src, device="cpu").pin_memory()
         hdout = torch.empty_like(dout, device="cpu").pin_memory()
-        hx.copy_(x)
+        hx.copy_(x_src)
         hdout.copy_(dout)
-        hdx = torch.empty_like(x, device="cpu").pin_memory()
-        wgp = wg.clone().requires_grad_(True)
-        wup = wu.clone().requires_grad_(True)
+        hdx = torch.empty_like(x_src, device="cpu").pin_memory()
+        wgp.grad = wup.grad = None
         # Double-buffered input pipeline, as a training loop's loader would run it:
         # while step i computes, the copy stream uploads step i+1's x and dout into
         # the other buffer set and a third stream downloads step i-1's dX.  Every
         # step still moves all of its inputs from the host and its result back.
         h2d_stream = torch.cuda.Stream(device=dev)
         d2h_stream = torch.cuda.Stream(device=dev)
-        x_dev = [torch.empty_like(x) for _ in range(2)]
+        x_dev = [torch.empty_like(x_src) for _ in range(2)]
         dout_dev = [torch.empty_like(dout) for _ in range(2)]
         dx_keep = [None, None]
         ready = [None, None]       # inputs of buffer b are on the device
@@ -411,7 +679,7 @@ def run_ours(args):
             xin = x_dev[b].detach().requires_grad_(True)
             wgp.grad = wup.grad = None
             if world > 1:
-                out = parallel.column_parallel_swiglu(xin, wgp, wup, fast_accum=fast)
+                out = parallel.column_parallel_swiglu(xin, wgp, wup, fast_accum=fast, row_sharded=rs)
             elif dtype == "fp16":
                 out = FastAccumFusedSwiGLU.apply(xin, wgp, wup)
             else:
@@ -451,17 +719,41 @@ def run_ours(args):
             tt = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             e2e_ms = float(tt.item())
+        # the dX that came back to the host against the device-resident run's
+        dx_host_rel = None
+        if dx_keep_for_e2e is not None:
+            want = dx_keep_for_e2e.view(bs, sq, dm)[rank * b_mine:(rank + 1) * b_mine] if rs else dx_keep_for_e2e.view(bs, sq, dm)
+            got = hdx.to(dev)
+            dx_host_rel = float(torch.linalg.norm(got.float() - want.float()) / torch.linalg.norm(want.float()))
+            if world > 1:
+                tt = torch.tensor([dx_host_rel], device=dev, dtype=torch.float64)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                dx_host_rel = float(tt.item())
+            if not dx_host_rel < PARITY_BOUND:
+                raise SystemExit(f"end-to-end dX differs from the device-resident run's by {dx_host_rel}")
+        if world == 1:
+            api = ("FastAccumFusedSwiGLU" if dtype == "fp16" else "FusedSwiGLU") + ".apply + backward"
+            note = ("every step uploads its x and dout from pinned host memory and downloads its dX; uploads for "
+                    "step i+1 and the download of step i overlap step i's kernels (double-buffered); weights "
+                    "stay resident")
+        else:
+            api = f"column_parallel_swiglu(row_sharded={rs}) + backward"
+            note = (("tokens sharded at the boundary: every step each rank uploads its T/N rows of x and its column "
+                     "shard of dout from pinned host memory, all-gathers x over NVLink, and downloads its T/N rows "
+                     "of the reduce-scattered dX; ") if rs else
+                    "every step each rank uploads the whole x and its column shard of dout and downloads the whole "
+                    "all-reduced dX; ") + \
+                "uploads for step i+1 and the download of step i overlap step i's kernels (double-buffered); " \
+                "weights stay resident; bytes are per rank"
         e2e = {"value": total_flops / e2e_ms / 1e9, "unit": "TFLOP/s",
                "h2d_bytes_per_step": hx.numel() * 2 + hdout.numel() * 2, "d2h_bytes_per_step": hdx.numel() * 2,
-               "ms_per_step": e2e_ms, "steps": n_e2e,
-               "api": ("FastAccumFusedSwiGLU" if dtype == "fp16" else "FusedSwiGLU") + ".apply + backward"
-               if world == 1 else "ColumnParallelSwiGLU.apply + backward",
-               "note": "every step uploads its x and dout from pinned host memory and downloads its dX; "
-                       "uploads for step i+1 and the download of step i overlap step i's kernels "
-                       "(double-buffered); weights stay resident"}
+               "ms_per_step": e2e_ms, "steps": n_e2e, "api": api, "note": note,
+               "dx_rel_to_device_resident_run": dx_host_rel}
         status = _lib.device_status()
         if status != 0:
             raise SystemExit(f"a kernel gave up on a bounded wait (status {status}) in the end-to-end loop")
+        del x_dev, dout_dev, dx_keep
+    del dx_keep_for_e2e
 
     # ---- same-box bar: the reference test's oracle expression on this GPU through
     # torch (two cuBLAS GEMMs + eager silu/mul, autograd backward).  Library code, timed
@@ -510,6 +802,10 @@ def run_ours(args):
             tf = gemm_flops_local / ms / 1e9
             kern[n] = {"ms": ms, "achieved": tf, "unit": "TFLOP/s", "bound": "tensor",
                        "frac": tf / peaks["bf16_tflops_sustained"]}
+    if world > 1:
+        kern["dw_dual_gemm"]["note"] = ("runs beside the NCCL all-reduce of dX; first column range on "
+                                        f"{_lib.get_option('sm_count') - parallel.comm_sms(world)} SMs")
+        kern["collective_exposed_after_dw"] = {"ms": tail_ms}
     dom = max((n for n in names if n != "gate_grad_elementwise"), key=lambda n: kern[n]["ms"])
     roofline = {
         "kernel": dom, "bound": "tensor", "achieved": kern[dom]["achieved"], "peak": peaks["bf16_tflops_sustained"],
@@ -518,7 +814,7 @@ def run_ours(args):
         "frac_of_burst": kern[dom]["achieved"] / peaks["bf16_tflops"],
         "frac_of_nominal": kern[dom]["achieved"] / NOMINAL_BF16_TFLOPS,
         "algorithmic_flops_per_launch": gemm_flops_local,
-        "traffic": NCU_TRAFFIC_BYTES.get((dom, args.workload, world)),
+        "traffic": load_dram_traffic(dom, args.workload, world),
         "algorithmic_hbm_bytes_per_launch": {
             "fwd_dual_gemm": 2.0 * (T * dm + 2 * dm * di_local + 3 * T * di_local),
             "dx_gemm": 2.0 * (2 * T * di_local + 2 * dm * di_local + T * dm),
@@ -530,28 +826,35 @@ def run_ours(args):
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
-        r = cpu_reference_run(bs, sq, dm, di, dtype, steps=3, warmup=1,
-                              sample_tokens=2048 if args.workload != "plumbing" else T, seed=args.seed)
-        cpu_baseline = {"value": r["tflops"], "unit": "TFLOP/s", "cores": r["threads"], "kind": "port",
-                        "sample": f"{r['tokens']} of {T} tokens per step, 3 steps after 1 warm-up, "
-                                  f"PyTorch SwiGLU + autograd on CPU, os.cpu_count()={os.cpu_count()}"}
+        tokens = cpu_sample_tokens(T, dm, di)
+        r = cpu_reference_run(bs, sq, dm, di, dtype, steps=2, warmup=1, sample_tokens=tokens, seed=args.seed)
+        cpu_baseline = cpu_baseline_object(r, T, 2, 1)
 
+    sm_mhz = clocks.get("sm_mhz") if clocks else None
     line = {
         "metric": "swiglu_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": dtype, "data": "synthetic",
         "config": {"workload": args.workload, "bs": bs, "sq": sq, "d_model": dm, "d_intermediate": di,
                    "parallelism": f"column-parallel d_intermediate x{world}" if world > 1 else "single GPU",
+                   "timed_path": ("column_parallel_swiglu forward + backward (the package's multi-GPU API), "
+                                  "x replicated, dX all-reduced" if world > 1 else
+                                  "the four launches of FusedSwiGLU forward + backward"),
                    "l2": "inputs larger than L2 (activations and weights exceed 126 MB); no flush",
+                   "preheat_s": args.preheat, "preheat_steps": pre_steps,
                    "comm_sms_reserved_during_dw": parallel.comm_sms(world) if world > 1 else 0,
-                   "accumulate": "fp16 accumulator in forward and dW, fp32 in dX" if fast else "fp32", "tile_options": {k: _lib.get_option(k) for k in ("cta_group", "nsub", "group_m")},
+                   "dw_columns_beside_collective": dw_split["first"], "dw_columns_local": di_local,
+                   "accumulate": "fp16 accumulator in forward and dW, fp32 in dX" if fast else "fp32",
+                   "tile_options": {k: _lib.get_option(k) for k in ("cta_group", "nsub", "group_m")},
                    "producer_pacing": pacing,
                    "tile_note": "0 = chosen per launch; this workload gets CTA pairs, 256x512 tiles"},
         "frac_of_nominal_bf16_peak": value / (NOMINAL_BF16_TFLOPS * world),
         "frac_of_measured_sustained": value / (peaks["bf16_tflops_sustained"] * world),
+        "ms_x_sm_mhz": ms_per_step * sm_mhz if sm_mhz else None,
         "fwd_tokens_per_s": fwd_tokens_per_s,
-        "gpu_launches": 4 * K,
+        "gpu_launches": n_launches,
         "clocks": clocks,
+        "parity": parity,
         "roofline": roofline,
         "e2e": e2e,
         "cpu_baseline": cpu_baseline,

@@ -95,13 +95,14 @@ def grad_input(dg: torch.Tensor, du: torch.Tensor, w_gate: torch.Tensor, w_up: t
 def grad_weights(
     x2d: torch.Tensor, dg: torch.Tensor, du: torch.Tensor, *, fast_accum: bool = False,
     out_gate: Optional[torch.Tensor] = None, out_up: Optional[torch.Tensor] = None,
-    columns: Optional[Tuple[int, int]] = None,
+    columns: Optional[Tuple[int, int]] = None, max_sms: int = 0,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """(dW_gate, dW_up), each (dm, di), reduced over all T rows of x2d.
 
     ``columns=(first, count)`` computes only that column range of both gradients
     (the rest of the output tensors is left as it is); pass ``out_gate``/``out_up``
-    to collect several ranges in one pair of tensors."""
+    to collect several ranges in one pair of tensors.  ``max_sms`` > 0 caps the SMs
+    this launch occupies (to leave room for a kernel that runs beside it)."""
     _require_cuda(x2d, dg, du)
     T, dm = x2d.shape
     di = dg.shape[1]
@@ -109,6 +110,8 @@ def grad_weights(
     dwu = out_up if out_up is not None else torch.empty((dm, di), device=x2d.device, dtype=x2d.dtype)
     acc = _lib.FSW_ACC_F16 if fast_accum else _lib.FSW_ACC_F32
     with torch.cuda.device(x2d.device):
+        if columns is None and max_sms > 0:
+            columns = (0, di)
         if columns is None:
             name = "fsw_backward_dw"
             rc = _lib.load().fsw_backward_dw(
@@ -119,7 +122,7 @@ def grad_weights(
             name = "fsw_backward_dw_columns"
             rc = _lib.load().fsw_backward_dw_columns(
                 x2d.data_ptr(), dg.data_ptr(), du.data_ptr(), dwg.data_ptr(), dwu.data_ptr(),
-                T, dm, di, int(columns[0]), int(columns[1]), _code(x2d), acc, _stream(x2d),
+                T, dm, di, int(columns[0]), int(columns[1]), int(max_sms), _code(x2d), acc, _stream(x2d),
             )
     _lib.check(name, rc)
     return dwg, dwu

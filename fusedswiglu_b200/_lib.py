@@ -21,7 +21,7 @@ SIGNATURES = {
     "fsw_backward_elementwise": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_void_p]),
     "fsw_backward_dx": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_backward_dw": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
-    "fsw_backward_dw_columns": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_int, c_int, c_void_p]),
+    "fsw_backward_dw_columns": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_int, c_int, c_int, c_void_p]),
     "fsw_backward": (c_int, [c_void_p] * 11 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_gemm": (c_int, [c_void_p] * 3 + [c_int64] * 3 + [c_int] * 4 + [c_void_p]),
     "fsw_backward_static_scratch": (c_int, [c_void_p] * 9 + [c_int64] * 3 + [c_int, c_int, c_void_p]),

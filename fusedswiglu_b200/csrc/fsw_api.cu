@@ -56,16 +56,16 @@ struct Options {
                                  // the two dies keep sharing operand panels in L2 (0 = off)
   int64_t pace_limit_us = 50;    // longest wait at one meeting point
   int64_t ew_blocks_per_sm = 32;  // grid cap of the elementwise kernel, per SM
-  // Debug overrides of the UMMA shared-memory descriptor fields (0 = built-in).
-  int64_t k_lbo = 0, k_sbo = 0, k_kadv = 0;
-  int64_t mn_lbo = 0, mn_sbo = 0, mn_kadv = 0;
 };
 static Options g_opt;
 
 // Status word the kernels write when a bounded wait gives up.
 __device__ uint32_t g_status_word;
-// Arrival counter and off switch of the producers' pacing (see Pacer).
-__device__ unsigned int g_pace[2];
+// Arrival counter and off switch of the producers' pacing (see Pacer).  Every paced
+// launch takes the next of kPaceSlots pairs, so launches that overlap on one device
+// (other streams, other host threads) do not disturb each other's counts.
+constexpr int kPaceSlots = 16;
+__device__ unsigned int g_pace[2 * kPaceSlots];
 // SM cycles and nanoseconds that CTA 0 of the last GEMM launch was resident.
 __device__ unsigned long long g_clk_probe[8];
 
@@ -79,6 +79,8 @@ struct DeviceInfo {
   uint32_t* status = nullptr;
   unsigned long long* clk_probe = nullptr;
   unsigned int* pace = nullptr;
+  unsigned int pace_next = 0;   // next slot of g_pace to hand out
+  unsigned int pace_last = 0;   // slot the last paced launch used
 };
 static DeviceInfo g_dev[kMaxDevices];
 static std::mutex g_mu;
@@ -184,6 +186,44 @@ static int ensure_device(DeviceInfo** out) {
 }
 
 // ------------------------------------------------------------- tensor maps --
+// Encoded maps are kept in a small direct-mapped cache keyed by everything the
+// encoding depends on, so a training loop that calls with the same buffers every
+// step encodes each map once.  (An encoding holds only the address and geometry,
+// so an entry stays valid even if the buffer is freed and the address reused for
+// a tensor of the same geometry.)
+struct MapKey {
+  const void* ptr;
+  uint64_t inner, outer, row_elems;
+  uint32_t box_inner, box_outer;
+  int32_t dtype, l2_promo;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && inner == o.inner && outer == o.outer && row_elems == o.row_elems &&
+           box_inner == o.box_inner && box_outer == o.box_outer && dtype == o.dtype &&
+           l2_promo == o.l2_promo;
+  }
+};
+constexpr int kMapCacheSlots = 256;
+struct MapCacheEntry {
+  bool valid = false;
+  MapKey key;
+  CUtensorMap map;
+};
+static MapCacheEntry g_map_cache[kMapCacheSlots];
+static std::mutex g_map_mu;
+static uint64_t g_map_hits = 0, g_map_misses = 0;
+
+static uint32_t map_slot(const MapKey& k) {
+  uint64_t h = reinterpret_cast<uintptr_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+  h ^= (k.inner * 0xC2B2AE3D27D4EB4Full) ^ (k.outer * 0x165667B19E3779F9ull) ^
+       (k.row_elems * 0x27D4EB2F165667C5ull) ^
+       ((uint64_t)k.box_outer << 40) ^ ((uint64_t)k.box_inner << 32) ^ ((uint64_t)k.dtype << 8) ^
+       (uint64_t)k.l2_promo;
+  h ^= h >> 29;
+  h *= 0xBF58476D1CE4E5B9ull;
+  h ^= h >> 32;
+  return (uint32_t)(h % kMapCacheSlots);
+}
+
 // Row-major (outer, inner) array of 16-bit elements; box = box_outer rows of 64
 // elements (128 bytes, 128-byte swizzle) or of 32 elements (64 bytes, 64-byte swizzle).
 // `row_elems` is the distance between rows in elements when the map covers a column
@@ -191,6 +231,17 @@ static int ensure_device(DeviceInfo** out) {
 static int make_map(CUtensorMap* m, const void* ptr, int dtype, uint64_t inner, uint64_t outer,
                     uint32_t box_outer, const char* what, uint32_t box_inner = 64,
                     uint64_t row_elems = 0) {
+  const MapKey key = {ptr, inner, outer, row_elems, box_inner, box_outer, dtype, (int32_t)g_opt.l2_promo};
+  const uint32_t slot = map_slot(key);
+  {
+    std::lock_guard<std::mutex> lock(g_map_mu);
+    const MapCacheEntry& e = g_map_cache[slot];
+    if (e.valid && e.key == key) {
+      *m = e.map;
+      ++g_map_hits;
+      return FSW_OK;
+    }
+  }
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {(row_elems ? row_elems : inner) * 2};
   cuuint32_t box[2] = {box_inner, box_outer};
@@ -199,13 +250,21 @@ static int make_map(CUtensorMap* m, const void* ptr, int dtype, uint64_t inner, 
       m, dtype == FSW_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
       const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
       box_inner == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
-      g_opt.l2_promo == 0   ? CU_TENSOR_MAP_L2_PROMOTION_NONE
-      : g_opt.l2_promo == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
-                            : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      key.l2_promo == 0   ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+      : key.l2_promo == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                          : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(FSW_ECUDA, "cuTensorMapEncodeTiled(%s: inner=%llu outer=%llu box_outer=%u) -> %d",
                 what, (unsigned long long)inner, (unsigned long long)outer, box_outer, (int)r);
+  {
+    std::lock_guard<std::mutex> lock(g_map_mu);
+    MapCacheEntry& e = g_map_cache[slot];
+    e.key = key;
+    e.map = *m;
+    e.valid = true;
+    ++g_map_misses;
+  }
   return FSW_OK;
 }
 
@@ -239,18 +298,14 @@ static void fill_operand_desc(int major, uint64_t* desc, uint32_t* kadv) {
   if (major == MAJOR_K) {
     // rows of 64 elements = one 128-byte swizzle row; 8-row groups 1024 B apart;
     // a K=16 step moves 32 bytes inside the swizzle row.
-    const uint32_t lbo = g_opt.k_lbo ? (uint32_t)g_opt.k_lbo : 16u;
-    const uint32_t sbo = g_opt.k_sbo ? (uint32_t)g_opt.k_sbo : 1024u;
-    *desc = make_sdesc(lbo, sbo);
-    *kadv = g_opt.k_kadv ? (uint32_t)g_opt.k_kadv : 32u;
+    *desc = make_sdesc(16u, 1024u);
+    *kadv = 32u;
   } else {
     // 64(MN) x 64(K) boxes: K rows of 128 bytes; 8-row K groups 1024 B apart
     // (stride offset); the next 64 MN elements are one whole box (8192 B) away
     // (leading offset); a K=16 step is 16 rows = 2048 bytes.
-    const uint32_t lbo = g_opt.mn_lbo ? (uint32_t)g_opt.mn_lbo : 8192u;
-    const uint32_t sbo = g_opt.mn_sbo ? (uint32_t)g_opt.mn_sbo : 1024u;
-    *desc = make_sdesc(lbo, sbo);
-    *kadv = g_opt.mn_kadv ? (uint32_t)g_opt.mn_kadv : 2048u;
+    *desc = make_sdesc(8192u, 1024u);
+    *kadv = 2048u;
   }
 }
 
@@ -307,7 +362,15 @@ static int check_common(int64_t T, int64_t dm, int64_t di, int dtype, int accum)
 struct TileChoice {
   int cg, nsub;
 };
-static TileChoice choose_tiles(int mode, int64_t rows, int64_t cols, const DeviceInfo* d) {
+// SMs a launch may occupy: the call's own cap if it has one, else the process-wide
+// "gemm_max_sms" option, else all of them.
+static int sm_budget(const DeviceInfo* d, int max_sms) {
+  int64_t cap = max_sms > 0 ? max_sms : g_opt.gemm_max_sms;
+  return (cap > 0 && cap < d->sm_count) ? (int)cap : d->sm_count;
+}
+
+static TileChoice choose_tiles(int mode, int64_t rows, int64_t cols, const DeviceInfo* d,
+                               int max_sms = 0) {
   const int want_cg = (int)g_opt.cta_group, want_ns = (int)g_opt.nsub;
   const int region_n = (mode == MODE_FWD || mode == MODE_DW) ? 128 : 256;
   const struct {
@@ -320,8 +383,8 @@ static TileChoice choose_tiles(int mode, int64_t rows, int64_t cols, const Devic
     if (want_cg != 0 && c.cg != want_cg) continue;
     if (want_ns != 0 && c.nsub != want_ns && !(c.cg == 1 && want_cg == 1)) continue;
     int workers = (c.cg == 2) ? d->max_pairs : d->sm_count;
-    if (g_opt.gemm_max_sms > 0) {
-      const int cap = (int)g_opt.gemm_max_sms / c.cg;
+    {
+      const int cap = sm_budget(d, max_sms) / c.cg;
       if (cap < workers) workers = cap < 1 ? 1 : cap;
     }
     const double tiles = (double)((rows + 128 * c.cg - 1) / (128 * c.cg)) *
@@ -338,7 +401,7 @@ static TileChoice choose_tiles(int mode, int64_t rows, int64_t cols, const Devic
 
 template <int MODE>
 static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t st,
-                    DeviceInfo* d, TileChoice tc) {
+                    DeviceInfo* d, TileChoice tc, int max_sms = 0) {
   const int cg = tc.cg;
   const int nsub = tc.nsub;
   const int tile_m = 128 * cg;
@@ -362,8 +425,7 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   if (tiles <= 0) return FSW_OK;
   if (tiles >= (1ll << 31)) return fail(FSW_EINVAL, "too many tiles");
   cudaError_t e;
-  int avail_sms = d->sm_count;
-  if (g_opt.gemm_max_sms > 0 && g_opt.gemm_max_sms < avail_sms) avail_sms = (int)g_opt.gemm_max_sms;
+  const int avail_sms = sm_budget(d, max_sms);
   // Rasterisation: tiles are issued group_m rows at a time, sweeping the columns.
   // The tiles in flight then form roughly a group_m x (workers / group_m) block and
   // read group_m A panels (256 rows each) + that many B panels (512 rows each) from
@@ -407,9 +469,15 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   {
     const long long workers = (cg == 2) ? avail_sms / 2 : avail_sms;
     if (g_opt.pace_kb > 0 && tiles > workers) {
-      p.pace = d->pace;
+      unsigned int slot;
+      {
+        std::lock_guard<std::mutex> lock(g_mu);
+        slot = d->pace_next++ % kPaceSlots;
+        d->pace_last = slot;
+      }
+      p.pace = d->pace + 2 * slot;
       p.pace_kb = (int)g_opt.pace_kb;
-      e = cudaMemsetAsync(d->pace, 0, 2 * sizeof(unsigned int), st);
+      e = cudaMemsetAsync(p.pace, 0, 2 * sizeof(unsigned int), st);
       if (e != cudaSuccess) return fail(FSW_ECUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(e));
     }
   }
@@ -610,18 +678,6 @@ int fsw_set_option(const char* name, int64_t value) {
   } else if (!strcmp(name, "ew_blocks_per_sm")) {
     if (value < 1 || value > 64) return fail(FSW_EINVAL, "ew_blocks_per_sm must be in [1, 64]");
     g_opt.ew_blocks_per_sm = value;
-  } else if (!strcmp(name, "k_lbo")) {
-    g_opt.k_lbo = value;
-  } else if (!strcmp(name, "k_sbo")) {
-    g_opt.k_sbo = value;
-  } else if (!strcmp(name, "k_kadv")) {
-    g_opt.k_kadv = value;
-  } else if (!strcmp(name, "mn_lbo")) {
-    g_opt.mn_lbo = value;
-  } else if (!strcmp(name, "mn_sbo")) {
-    g_opt.mn_sbo = value;
-  } else if (!strcmp(name, "mn_kadv")) {
-    g_opt.mn_kadv = value;
   } else {
     return fail(FSW_EINVAL, "unknown option '%s'", name);
   }
@@ -649,15 +705,12 @@ int64_t fsw_get_option(const char* name) {
     if (ensure_device(&d) != FSW_OK) return -1;
     unsigned int v[2] = {0, 0};
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    if (cudaMemcpy(v, d->pace, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (cudaMemcpy(v, d->pace + 2 * d->pace_last, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess)
+      return -1;
     return v[1];
   }
-  if (!strcmp(name, "k_lbo")) return g_opt.k_lbo;
-  if (!strcmp(name, "k_sbo")) return g_opt.k_sbo;
-  if (!strcmp(name, "k_kadv")) return g_opt.k_kadv;
-  if (!strcmp(name, "mn_lbo")) return g_opt.mn_lbo;
-  if (!strcmp(name, "mn_sbo")) return g_opt.mn_sbo;
-  if (!strcmp(name, "mn_kadv")) return g_opt.mn_kadv;
+  if (!strcmp(name, "map_cache_hits")) return (int64_t)g_map_hits;
+  if (!strcmp(name, "map_cache_misses")) return (int64_t)g_map_misses;
   if (!strcmp(name, "last_sm_khz")) {
     // Synchronises; average SM clock (kHz) seen by CTA 0 of the last GEMM launch.
     DeviceInfo* d = nullptr;
@@ -781,9 +834,10 @@ int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const vo
 // full arrays, whose rows are di elements long.
 static int backward_dw_columns(const void* x, const void* dg, const void* du, void* dw_gate,
                                void* dw_up, int64_t T, int64_t dm, int64_t di, int64_t col0,
-                               int64_t ncols, int dtype, int accum, void* stream) {
+                               int64_t ncols, int max_sms, int dtype, int accum, void* stream) {
   int rc = check_common(T, dm, di, dtype, accum);
   if (rc != FSW_OK) return rc;
+  if (max_sms < 0) return fail(FSW_EINVAL, "max_sms must be >= 0 (0 = no cap of its own)");
   if (col0 < 0 || ncols < 0 || col0 + ncols > di || (col0 % 8) != 0 || (ncols % 8) != 0)
     return fail(FSW_EINVAL, "column range [%lld, +%lld) must lie in [0, %lld) and be multiples of 8",
                 (long long)col0, (long long)ncols, (long long)di);
@@ -820,18 +874,19 @@ static int backward_dw_columns(const void* x, const void* dg, const void* du, vo
   p.ldc = (int)di;
   p.num_k_blocks = (int)((T + 63) / 64);
   return run_gemm<MODE_DW>(p, (int)dm, dtype, accum == FSW_ACC_F16, st, d,
-                           choose_tiles(MODE_DW, dm, ncols, d));
+                           choose_tiles(MODE_DW, dm, ncols, d, max_sms), max_sms);
 }
 
 int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate, void* dw_up,
                     int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream) {
-  return backward_dw_columns(x, dg, du, dw_gate, dw_up, T, dm, di, 0, di, dtype, accum, stream);
+  return backward_dw_columns(x, dg, du, dw_gate, dw_up, T, dm, di, 0, di, 0, dtype, accum, stream);
 }
 
 int fsw_backward_dw_columns(const void* x, const void* dg, const void* du, void* dw_gate,
                             void* dw_up, int64_t T, int64_t dm, int64_t di, int64_t col0,
-                            int64_t ncols, int dtype, int accum, void* stream) {
-  return backward_dw_columns(x, dg, du, dw_gate, dw_up, T, dm, di, col0, ncols, dtype, accum, stream);
+                            int64_t ncols, int max_sms, int dtype, int accum, void* stream) {
+  return backward_dw_columns(x, dg, du, dw_gate, dw_up, T, dm, di, col0, ncols, max_sms, dtype,
+                             accum, stream);
 }
 
 int fsw_backward(const void* dout, const void* x, const void* w_gate, const void* w_up,

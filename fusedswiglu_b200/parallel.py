@@ -11,11 +11,19 @@ process group (one process per GPU).  Rank r holds columns
     NCCL's stream while the dW GEMM - which does not depend on dX - computes; the
     backward joins the two before it returns.
 
+With ``row_sharded=True`` the tokens are sharded as well at the boundary of the
+call (sequence parallel): rank r passes rows ``[r*T/P, (r+1)*T/P)`` of x, the
+forward all-gathers them over NVLink, and the backward ends in a reduce-scatter of
+dX, so each rank gets back the gradient of its own rows only.  Per-rank host
+traffic and the collective's wire bytes then shrink with the number of ranks
+(``(P-1)/P`` of dX crosses NVLink instead of ``2(P-1)/P``).
+
 The reference (fattorib/fusedswiglu) has no multi-GPU mode; this follows the
 standard tensor-parallel MLP split and keeps the single-GPU numerics per shard.
 """
 from __future__ import annotations
 
+import contextlib
 import os
 from typing import Optional, Tuple
 
@@ -54,15 +62,17 @@ DW_SPLIT_ALIGN = 256  # columns per dW tile
 
 
 def plan_dw_split(T: int, dm: int, di_local: int, world_size: int, sm_count: int, reserve: int,
-                  elem_bytes: int = 2) -> int:
+                  elem_bytes: int = 2, collective: str = "all_reduce") -> int:
     """Columns of the local dW GEMM to run on ``sm_count - reserve`` SMs beside the
-    all-reduce of dX (T x dm elements); the remaining columns run afterwards on all
-    SMs.  The first part is sized to last 1.1x the estimated all-reduce time; returns
+    collective on dX (T x dm elements; ``"all_reduce"`` or ``"reduce_scatter"``, which
+    moves half the bytes); the remaining columns run afterwards on all SMs.  The
+    first part is sized to last 1.1x the estimated collective time; returns
     ``di_local`` when the whole GEMM is needed to cover it."""
     if world_size <= 1 or reserve <= 0:
         return 0
     bus = ALLREDUCE_BUS_BYTES_PER_S.get(world_size, ALLREDUCE_BUS_BYTES_PER_S_OTHER)
-    t_ar = 2.0 * (world_size - 1) / world_size * T * dm * elem_bytes / bus
+    passes = 2.0 if collective == "all_reduce" else 1.0
+    t_ar = passes * (world_size - 1) / world_size * T * dm * elem_bytes / bus
     t_ar += ALLREDUCE_FIXED_S
     rate = GEMM_SUSTAINED_FLOPS * max(1, sm_count - reserve) / sm_count
     t_dw = 4.0 * T * dm * di_local / rate
@@ -112,8 +122,9 @@ class _CudaBackend:
     gemm = staticmethod(_launch.gemm)
 
     @staticmethod
-    def grad_weights_beside_collective(x2d, dg, du, *, fast_accum=False, world_size=2, work=None):
-        """dW GEMM while the all-reduce of dX (``work``) is in flight.
+    def grad_weights_beside_collective(x2d, dg, du, *, fast_accum=False, world_size=2, work=None,
+                                       collective="all_reduce"):
+        """dW GEMM while the collective on dX (``work``) is in flight.
 
         NCCL's kernel makes no progress until all of its CTAs are resident, so the
         columns of dW that overlap it run on all but comm_sms(world_size) SMs.  When
@@ -123,62 +134,86 @@ class _CudaBackend:
         reserve = comm_sms(world_size)
         if reserve <= 0:
             return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum)
-        sms = _lib.get_option("sm_count")
+        with torch.cuda.device(x2d.device) if x2d.is_cuda else contextlib.nullcontext():
+            sms = _lib.get_option("sm_count")  # of the device the tensors live on
         T, dm = x2d.shape
         di = dg.shape[1]
-        first = plan_dw_split(T, dm, di, world_size, sms, reserve, x2d.element_size()) if work is not None else di
-        _lib.set_option("gemm_max_sms", max(2, sms - reserve))
-        try:
-            if first >= di:
-                return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum)
-            dwg, dwu = _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum, columns=(0, first))
-        finally:
-            _lib.set_option("gemm_max_sms", 0)
+        first = (plan_dw_split(T, dm, di, world_size, sms, reserve, x2d.element_size(), collective)
+                 if work is not None else di)
+        cap = max(2, sms - reserve)  # an argument of this one launch, not process-wide state
+        if first >= di:
+            return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum, max_sms=cap)
+        dwg, dwu = _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum, columns=(0, first), max_sms=cap)
         work.wait()  # stream-level: the rest starts when the collective's kernel has left the SMs
         return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum, out_gate=dwg, out_up=dwu,
                                     columns=(first, di - first))
 
 
-class ColumnParallelSwiGLU(Function):
-    """``ColumnParallelSwiGLU.apply(x, w_gate_shard, w_up_shard, group=None)``.
+def _reduce_dx(dx, group, row_sharded):
+    """Start the one collective of the backward.  Returns (work, result): the
+    all-reduce works in place; the reduce-scatter leaves this rank's rows of the
+    sum in a new (T/P, dm) tensor."""
+    if not row_sharded:
+        return dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group, async_op=True), dx
+    world = dist.get_world_size(group)
+    mine = torch.empty((dx.shape[0] // world, dx.shape[1]), device=dx.device, dtype=dx.dtype)
+    return dist.reduce_scatter_tensor(mine, dx, op=dist.ReduceOp.SUM, group=group, async_op=True), mine
 
-    x: (bs, sq, d_model), identical on every rank.  Weight shards:
-    (d_model, d_intermediate / world_size).  Returns this rank's slice of out.
-    The gradient returned for x is the full, all-reduced dX."""
+
+class ColumnParallelSwiGLU(Function):
+    """``ColumnParallelSwiGLU.apply(x, w_gate_shard, w_up_shard, group=None, fast_accum=False,
+    backend=None, row_sharded=False)``.
+
+    Weight shards: (d_model, d_intermediate / world_size).  Returns this rank's
+    column slice of out for ALL tokens.
+
+    row_sharded=False: x (bs, sq, d_model) is identical on every rank; the gradient
+    returned for x is the full, all-reduced dX.
+    row_sharded=True: x (bs/P, sq, d_model) holds this rank's tokens (rank-major in
+    the flattened token order); they are all-gathered for the forward and the
+    gradient returned for x is this rank's rows of the reduce-scattered dX."""
 
     @staticmethod
-    def forward(ctx, x, w_gate_shard, w_up_shard, group=None, fast_accum=False, backend=None):
+    def forward(ctx, x, w_gate_shard, w_up_shard, group=None, fast_accum=False, backend=None,
+                row_sharded=False):
         backend = backend or _CudaBackend
         assert x.ndim == 3 and w_gate_shard.ndim == 2, "Incorrect number of dimensions for LHS or RHS"
         assert w_gate_shard.shape == w_up_shard.shape, "Expected both weight matrices to have same shape"
         assert x.shape[2] == w_up_shard.shape[0], "Dimension mismatch between x and the weight shards"
         bs, sq, dm = x.shape
         x2d = x.contiguous().view(bs * sq, dm)
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        sharded = bool(row_sharded) and world > 1
+        if sharded:
+            x_all = torch.empty((world * bs * sq, dm), device=x2d.device, dtype=x2d.dtype)
+            dist.all_gather_into_tensor(x_all, x2d, group=group)
+            x2d = x_all
         wg = w_gate_shard.contiguous()
         wu = w_up_shard.contiguous()
         out, g, u = backend.forward(x2d, wg, wu, fast_accum=fast_accum, save_activations=True)
         ctx.save_for_backward(x2d, wg, wu, g, u)
-        ctx.meta = (bs, sq, dm, group, fast_accum, backend)
-        return out.view(bs, sq, wg.shape[1])
+        ctx.meta = (bs, sq, dm, group, fast_accum, backend, sharded)
+        return out.view((world if sharded else 1) * bs, sq, wg.shape[1])
 
     @staticmethod
     def backward(ctx, grad_output):
         x2d, wg, wu, g, u = ctx.saved_tensors
-        bs, sq, dm, group, fast_accum, backend = ctx.meta
-        dout = grad_output.contiguous().view(bs * sq, wg.shape[1])
+        bs, sq, dm, group, fast_accum, backend, sharded = ctx.meta
+        dout = grad_output.contiguous().view(x2d.shape[0], wg.shape[1])
         dg, du = backend.gate_grad(dout, g, u)
         dx = backend.grad_input(dg, du, wg, wu)
         work = None
         if dist.is_initialized() and dist.get_world_size(group) > 1:
-            work = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group, async_op=True)
+            work, dx = _reduce_dx(dx, group, sharded)
         if work is not None and hasattr(backend, "grad_weights_beside_collective"):
             dwg, dwu = backend.grad_weights_beside_collective(
-                x2d, dg, du, fast_accum=fast_accum, world_size=dist.get_world_size(group), work=work)
+                x2d, dg, du, fast_accum=fast_accum, world_size=dist.get_world_size(group), work=work,
+                collective="reduce_scatter" if sharded else "all_reduce")
         else:
             dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=fast_accum)
         if work is not None:
             work.wait()
-        return dx.view(bs, sq, dm), dwg, dwu, None, None, None
+        return dx.view(bs, sq, dm), dwg, dwu, None, None, None, None
 
 
 def shard_rows(w: torch.Tensor, rank: int, world_size: int) -> torch.Tensor:
@@ -241,6 +276,7 @@ class TensorParallelSwiGLUMLP(Function):
 
 def column_parallel_swiglu(
     x: torch.Tensor, w_gate_shard: torch.Tensor, w_up_shard: torch.Tensor,
-    group: Optional[dist.ProcessGroup] = None, fast_accum: bool = False,
+    group: Optional[dist.ProcessGroup] = None, fast_accum: bool = False, row_sharded: bool = False,
+    backend=None,
 ) -> torch.Tensor:
-    return ColumnParallelSwiGLU.apply(x, w_gate_shard, w_up_shard, group, fast_accum, None)
+    return ColumnParallelSwiGLU.apply(x, w_gate_shard, w_up_shard, group, fast_accum, backend, row_sharded)

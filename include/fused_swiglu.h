@@ -79,14 +79,17 @@ int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate
  * fsw_backward_dw restricted to columns [col0, col0 + ncols) of dw_gate and dw_up
  * (col0 and ncols multiples of 8).  All pointers are to the FULL arrays: dg and du
  * (T, di), dw_gate and dw_up (dm, di); only the named columns are read and written,
- * and they get exactly the values fsw_backward_dw would give them.  Lets a caller cut
- * the weight-gradient GEMM into pieces, e.g. to run one piece beside a collective on
- * fewer SMs ("gemm_max_sms") and the rest on the whole GPU.  No counterpart in the
- * reference, whose fused_bmm always covers all of d_intermediate.
+ * and they get exactly the values fsw_backward_dw would give them.  `max_sms` > 0
+ * caps the SMs this one launch occupies (0 = no cap of its own; the process-wide
+ * "gemm_max_sms" option, if set, then applies).  Lets a caller cut the
+ * weight-gradient GEMM into pieces, e.g. to run one piece beside a collective on
+ * fewer SMs and the rest on the whole GPU, without touching process-wide state.
+ * No counterpart in the reference, whose fused_bmm always covers all of
+ * d_intermediate.
  */
 int fsw_backward_dw_columns(const void* x, const void* dg, const void* du, void* dw_gate,
                             void* dw_up, int64_t T, int64_t dm, int64_t di, int64_t col0,
-                            int64_t ncols, int dtype, int accum, void* stream);
+                            int64_t ncols, int max_sms, int dtype, int accum, void* stream);
 
 /*
  * Whole backward on one stream: elementwise step into the caller's scratch
@@ -165,7 +168,14 @@ int fsw_query_device(int device, int* sm_count, int* cc_major, int* cc_minor,
 int64_t fsw_status(void);
 
 /*
- * Tuning and debugging knobs, process-wide.  Main names: "cta_group" (1 or 2 CTAs
+ * Tuning and debugging knobs.  They are PROCESS-WIDE: a value set here applies to
+ * every later call from any thread on any device, so a host with several threads
+ * should set them once at start-up (per-call needs, like an SM cap for one launch,
+ * are arguments of the entry points instead).  Apart from these options the
+ * library keeps only caches (device attributes, encoded tensor maps) and, per
+ * device, one status word (fsw_status), one clock probe ("last_sm_khz") and a ring
+ * of pacing counters; entry points may be called concurrently from several threads
+ * and on several streams and devices.  Main names: "cta_group" (1 or 2 CTAs
  * per MMA, 0 = automatic), "nsub" (1 or 2 accumulator regions per tile, 0 =
  * automatic), "group_m" (tile rasterisation group height in tiles, 0 = automatic),
  * "gemm_max_sms" (cap on the SMs a GEMM launch occupies, 0 = all; used to leave room
@@ -176,7 +186,7 @@ int64_t fsw_status(void);
  * "l2_out" (L2 eviction priority of operand loads and forward stores: 0 normal,
  * 1 evict first, 2 evict last), "ew_blocks_per_sm".  Read-only facts through
  * fsw_get_option: "sm_count", "max_pairs", "stages", "last_sm_khz", "pace_off" (1 if
- * the last paced launch gave its pacing up).  Returns FSW_EINVAL for an unknown name
+ * the last paced launch gave its pacing up), "map_cache_hits", "map_cache_misses".  Returns FSW_EINVAL for an unknown name
  * or value.  fsw_get_option returns the current value or -1.
  */
 int fsw_set_option(const char* name, int64_t value);

@@ -54,10 +54,13 @@ def test_argument_errors_are_reported_not_raised_across_the_abi():
     rc = lib.fsw_forward(None, None, None, None, None, None, 8, 64, 64, 0, 0, None)
     assert rc == -1 and "required" in _lib.last_error()
     # column range outside the array, or not a multiple of 8
-    rc = lib.fsw_backward_dw_columns(None, None, None, None, None, 8, 64, 64, 32, 40, 0, 0, None)
+    rc = lib.fsw_backward_dw_columns(None, None, None, None, None, 8, 64, 64, 32, 40, 0, 0, 0, None)
     assert rc == -1 and "column range" in _lib.last_error()
-    rc = lib.fsw_backward_dw_columns(None, None, None, None, None, 8, 64, 64, 4, 8, 0, 0, None)
+    rc = lib.fsw_backward_dw_columns(None, None, None, None, None, 8, 64, 64, 4, 8, 0, 0, 0, None)
     assert rc == -1 and "column range" in _lib.last_error()
+    # a negative SM cap
+    rc = lib.fsw_backward_dw_columns(None, None, None, None, None, 8, 64, 64, 0, 8, -1, 0, 0, None)
+    assert rc == -1 and "max_sms" in _lib.last_error()
     # misaligned pointer
     rc = lib.fsw_backward_elementwise(8, 16, 16, 16, 16, 64, 0, None)
     assert rc == -1 and "aligned" in _lib.last_error()

@@ -51,6 +51,22 @@ def _worker(rank, world, port, q):
         def rel(a, b):
             return (torch.linalg.norm(a.float() - b.float()) / torch.linalg.norm(b.float())).item()
 
+        # tokens sharded at the boundary too: all-gather of x, reduce-scatter of dX
+        b0, b1 = rank * bs // world, (rank + 1) * bs // world
+        xs_ = x0[b0:b1].clone().requires_grad_(True)
+        wg2 = parallel.shard_columns(wg0, rank, world).requires_grad_(True)
+        wu2 = parallel.shard_columns(wu0, rank, world).requires_grad_(True)
+        out2 = parallel.column_parallel_swiglu(xs_, wg2, wu2, row_sharded=True)
+        out2.backward(dout[..., lo:hi].contiguous())
+        torch.cuda.synchronize()
+        row_sharded = {
+            "out_equal": bool(torch.equal(out2.detach(), out.detach())),
+            "dwg_equal": bool(torch.equal(wg2.grad, wg.grad)),
+            "dwu_equal": bool(torch.equal(wu2.grad, wu.grad)),
+            "dx_shape_ok": tuple(xs_.grad.shape) == (bs // world, sq, dm),
+            "dx_rel": rel(xs_.grad, xr.grad[b0:b1]),
+        }
+
         # whole MLP block, tensor parallel vs single GPU
         from fusedswiglu_b200.mlp import FusedSwiGLUMLP
 
@@ -72,6 +88,7 @@ def _worker(rank, world, port, q):
 
         q.put((rank, {
             "mlp": mlp,
+            "row_sharded": row_sharded,
             "out_equal": bool(torch.equal(out_full, ref.detach())),
             "dwg_equal": bool(torch.equal(wg.grad, wgr.grad[:, lo:hi])),
             "dwu_equal": bool(torch.equal(wu.grad, wur.grad[:, lo:hi])),
@@ -103,6 +120,9 @@ def test_two_gpu_column_parallel_matches_single_gpu():
         # dX: each rank rounds its partial sum to bf16 before the all-reduce
         assert r["dx_rel"] < 1e-2, (rank, r)
         assert r["status"] == 0
+        rs = r["row_sharded"]
+        assert rs["out_equal"] and rs["dwg_equal"] and rs["dwu_equal"] and rs["dx_shape_ok"], (rank, rs)
+        assert rs["dx_rel"] < 1e-2, (rank, rs)
         # tensor-parallel MLP: partial sums are rounded per rank before the all-reduce
         for k, v in r["mlp"].items():
             assert v < 1e-2, (rank, k, r["mlp"])

@@ -229,34 +229,28 @@ def test_plan_of_the_dw_split_beside_the_all_reduce():
 
 
 def test_dw_beside_collective_call_sequence(monkeypatch):
-    """Host logic of the dW launch beside the all-reduce, with the library and the
-    launchers replaced by recorders (no GPU): SMs are reserved only for the first
-    column range, the stream waits for the collective before the rest, and the
-    reservation is lifted even if a launch raises."""
+    """Host logic of the dW launch beside the collective, with the library and the
+    launchers replaced by recorders (no GPU): the SM cap is an argument of the first
+    launch only (no process-wide option is touched), the stream waits for the
+    collective before the rest, and the rest runs uncapped."""
     import torch
     from fusedswiglu_b200 import parallel
 
     log = []
-    opts = {"sm_count": 148, "gemm_max_sms": 0}
 
     class FakeLib:
         @staticmethod
         def get_option(name):
-            return opts[name]
+            return {"sm_count": 148}[name]
 
         @staticmethod
-        def set_option(name, value):
-            opts[name] = value
-            log.append(("set", name, value))
+        def set_option(name, value):  # must not be called
+            raise AssertionError(f"process-wide option {name} was set")
 
     class FakeLaunch:
-        fail = False
-
         @staticmethod
-        def grad_weights(x2d, dg, du, *, fast_accum=False, out_gate=None, out_up=None, columns=None):
-            if FakeLaunch.fail:
-                raise RuntimeError("launch failed")
-            log.append(("dw", columns, opts["gemm_max_sms"], out_gate is not None))
+        def grad_weights(x2d, dg, du, *, fast_accum=False, out_gate=None, out_up=None, columns=None, max_sms=0):
+            log.append(("dw", columns, max_sms, out_gate is not None))
             return (out_gate if out_gate is not None else "dwg"), (out_up if out_up is not None else "dwu")
 
     class Work:
@@ -265,23 +259,82 @@ def test_dw_beside_collective_call_sequence(monkeypatch):
 
     monkeypatch.setattr(parallel, "_lib", FakeLib)
     monkeypatch.setattr(parallel, "_launch", FakeLaunch)
-    x2d, dg = torch.empty(65536, 8192, device="meta", dtype=torch.bfloat16), torch.empty(65536, 7168, device="meta", dtype=torch.bfloat16)
+    x2d, dg = torch.empty(65536, 8192, dtype=torch.bfloat16, device="meta"), torch.empty(65536, 7168, dtype=torch.bfloat16, device="meta")
     first = parallel.plan_dw_split(65536, 8192, 7168, 4, 148, 32)
     out = parallel._CudaBackend.grad_weights_beside_collective(x2d, dg, dg, world_size=4, work=Work())
     assert out == ("dwg", "dwu")
-    assert log == [("set", "gemm_max_sms", 116), ("dw", (0, first), 116, False), ("set", "gemm_max_sms", 0),
-                   ("wait",), ("dw", (first, 7168 - first), 0, True)]
+    assert log == [("dw", (0, first), 116, False), ("wait",), ("dw", (first, 7168 - first), 0, True)]
+    # a reduce-scatter moves half the bytes of an all-reduce: a smaller first part
+    log.clear()
+    first_rs = parallel.plan_dw_split(65536, 8192, 7168, 4, 148, 32, collective="reduce_scatter")
+    assert 0 < first_rs < first
+    parallel._CudaBackend.grad_weights_beside_collective(x2d, dg, dg, world_size=4, work=Work(),
+                                                         collective="reduce_scatter")
+    assert log == [("dw", (0, first_rs), 116, False), ("wait",), ("dw", (first_rs, 7168 - first_rs), 0, True)]
     # the collective outlasts the GEMM (8 ranks, 8B shape): one launch, all of it on the reduced SM count
     log.clear()
-    x2d, dg = torch.empty(32768, 4096, device="meta", dtype=torch.bfloat16), torch.empty(32768, 1792, device="meta", dtype=torch.bfloat16)
+    x2d, dg = torch.empty(32768, 4096, dtype=torch.bfloat16, device="meta"), torch.empty(32768, 1792, dtype=torch.bfloat16, device="meta")
     parallel._CudaBackend.grad_weights_beside_collective(x2d, dg, dg, world_size=8, work=Work())
-    assert log == [("set", "gemm_max_sms", 116), ("dw", None, 116, False), ("set", "gemm_max_sms", 0)]
-    # a failing launch still lifts the reservation
-    log.clear()
-    FakeLaunch.fail = True
-    with pytest.raises(RuntimeError):
-        parallel._CudaBackend.grad_weights_beside_collective(x2d, dg, dg, world_size=8, work=Work())
-    assert opts["gemm_max_sms"] == 0
+    assert log == [("dw", None, 116, False)]
+
+
+def _row_sharded_worker(rank, world, port, q):
+    sys.path.insert(0, str(REPO))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fusedswiglu_b200 import parallel
+        from oracle import swiglu_oracle as orc
+
+        torch.manual_seed(0)
+        bs, sq, dm, di = 4, 16, 64, 128
+        x = torch.randn(bs, sq, dm).bfloat16()
+        wg = (torch.randn(dm, di) / dm ** 0.5).bfloat16()
+        wu = (torch.randn(dm, di) / dm ** 0.5).bfloat16()
+        dout = torch.randn(bs, sq, di).bfloat16()
+        lo, hi = parallel.shard_bounds(di, rank, world)
+        b0, b1 = rank * bs // world, (rank + 1) * bs // world
+        x_mine = x[b0:b1].clone().requires_grad_(True)
+        wg_s = parallel.shard_columns(wg, rank, world).requires_grad_(True)
+        wu_s = parallel.shard_columns(wu, rank, world).requires_grad_(True)
+        out_s = parallel.column_parallel_swiglu(x_mine, wg_s, wu_s, row_sharded=True, backend=OracleBackend)
+        assert out_s.shape == (bs, sq, hi - lo)
+        out_s.backward(dout[..., lo:hi].contiguous())
+        assert x_mine.grad.shape == (bs // world, sq, dm)
+        out_full = parallel.unshard_columns(out_s.detach())
+
+        xr = x.clone().requires_grad_(True)
+        wgr = wg.clone().requires_grad_(True)
+        wur = wu.clone().requires_grad_(True)
+        ref = orc.swiglu_ref_torch(xr, wgr, wur)
+        ref.backward(dout)
+
+        def rel(a, b):
+            return (torch.linalg.norm(a.float() - b.float()) / torch.linalg.norm(b.float())).item()
+
+        q.put((rank, {"out": rel(out_full, ref), "dx": rel(x_mine.grad, xr.grad[b0:b1]),
+                      "dwg": rel(wg_s.grad, wgr.grad[:, lo:hi]), "dwu": rel(wu_s.grad, wur.grad[:, lo:hi])}))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_row_sharded_mode_matches_unsharded_reference():
+    """Tokens sharded at the boundary: all-gather of x in forward, reduce-scatter of
+    dX in backward; every rank gets the gradient of its own rows."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_row_sharded_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, errs in results:
+        for k, v in errs.items():
+            assert v < 1e-2, (rank, k, errs)
 
 
 def test_rank_that_never_joins_ends_the_collective_with_an_error():
