@@ -69,9 +69,12 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--preheat", type=float, default=1.0, metavar="SECONDS",
+    ap.add_argument("--preheat", type=float, default=3.0, metavar="SECONDS",
                     help="run the same step loop for this long before the warm-up steps, so that short timed "
                          "regions (many GPUs) are measured at the power-capped clock like long ones")
+    ap.add_argument("--comm-ctas", type=int, default=16, metavar="N",
+                    help="N>1: CTAs NCCL may use for the dX collective (= SMs the dW GEMM leaves free beside it); "
+                         "0 = NCCL's own choice on the default group with the default reservation")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
@@ -411,6 +414,10 @@ def run_ours(args):
 
     from fusedswiglu_b200 import FastAccumFusedSwiGLU, FusedSwiGLU, _launch, _lib, parallel
 
+    # The dX collective runs on a group whose NCCL kernels are capped to as many CTAs
+    # as the dW GEMM leaves SMs free for them.
+    group = parallel.new_collective_group(max_ctas=args.comm_ctas) if world > 1 and args.comm_ctas > 0 else None
+
     _lib.load()
     for item in args.opt:
         name, _, value = item.partition("=")
@@ -449,7 +456,7 @@ def run_ours(args):
     names = ["fwd_dual_gemm", "gate_grad_elementwise", "dx_gemm", "dw_dual_gemm"]
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(K)]
     launches = {"n": 0}
-    dw_split = {"first": None}
+    dw_split = {"first": None, "collective_ms": None}
 
     def counted(fn):
         def wrapper(*a, **kw):
@@ -496,10 +503,11 @@ def run_ours(args):
         def grad_weights_beside_collective(x2d_, dg, du, **kw):
             Marked._mark(3)
             if dw_split["first"] is None and kw.get("work") is not None:
+                dw_split["collective_ms"] = (kw.get("collective_s") or 0.0) * 1e3
                 dw_split["first"] = parallel.plan_dw_split(
                     x2d_.shape[0], x2d_.shape[1], dg.shape[1], kw.get("world_size", world),
-                    _lib.get_option("sm_count"), parallel.comm_sms(world), x2d_.element_size(),
-                    kw.get("collective", "all_reduce"))
+                    _lib.get_option("sm_count"), parallel.comm_sms(world, kw.get("group")), x2d_.element_size(),
+                    kw.get("collective", "all_reduce"), kw.get("collective_s"))
             r = parallel._CudaBackend.grad_weights_beside_collective(x2d_, dg, du, **kw)
             Marked._mark(4)
             return r
@@ -523,7 +531,7 @@ def run_ours(args):
         xin = x.detach().requires_grad_(True)
         wgp.grad = wup.grad = None
         Marked.marks = marks
-        out = parallel.column_parallel_swiglu(xin, wgp, wup, fast_accum=fast, backend=Marked)
+        out = parallel.column_parallel_swiglu(xin, wgp, wup, group=group, fast_accum=fast, backend=Marked)
         out.backward(dout)
         if marks: marks[5].record()
         Marked.marks = None
@@ -679,7 +687,7 @@ def run_ours(args):
             xin = x_dev[b].detach().requires_grad_(True)
             wgp.grad = wup.grad = None
             if world > 1:
-                out = parallel.column_parallel_swiglu(xin, wgp, wup, fast_accum=fast, row_sharded=rs)
+                out = parallel.column_parallel_swiglu(xin, wgp, wup, group=group, fast_accum=fast, row_sharded=rs)
             elif dtype == "fp16":
                 out = FastAccumFusedSwiGLU.apply(xin, wgp, wup)
             else:
@@ -804,7 +812,7 @@ def run_ours(args):
                        "frac": tf / peaks["bf16_tflops_sustained"]}
     if world > 1:
         kern["dw_dual_gemm"]["note"] = ("runs beside the NCCL all-reduce of dX; first column range on "
-                                        f"{_lib.get_option('sm_count') - parallel.comm_sms(world)} SMs")
+                                        f"{_lib.get_option('sm_count') - parallel.comm_sms(world, group)} SMs")
         kern["collective_exposed_after_dw"] = {"ms": tail_ms}
     dom = max((n for n in names if n != "gate_grad_elementwise"), key=lambda n: kern[n]["ms"])
     roofline = {
@@ -842,8 +850,9 @@ def run_ours(args):
                                   "the four launches of FusedSwiGLU forward + backward"),
                    "l2": "inputs larger than L2 (activations and weights exceed 126 MB); no flush",
                    "preheat_s": args.preheat, "preheat_steps": pre_steps,
-                   "comm_sms_reserved_during_dw": parallel.comm_sms(world) if world > 1 else 0,
+                   "comm_sms_reserved_during_dw": parallel.comm_sms(world, group) if world > 1 else 0,
                    "dw_columns_beside_collective": dw_split["first"], "dw_columns_local": di_local,
+                   "collective_ms_measured_alone": dw_split["collective_ms"],
                    "accumulate": "fp16 accumulator in forward and dW, fp32 in dX" if fast else "fp32",
                    "tile_options": {k: _lib.get_option(k) for k in ("cta_group", "nsub", "group_m")},
                    "producer_pacing": pacing,

@@ -33,27 +33,79 @@ from torch.autograd import Function
 
 from . import _launch, _lib
 
-# SMs left free for the all-reduce kernel while the dW GEMM runs.  The GEMMs are
+# SMs left free for the collective's kernel while the dW GEMM runs.  The GEMMs are
 # persistent and would otherwise occupy every SM, so that NCCL's kernel could not
 # start before they finish and the collective would not overlap anything.  NCCL's
-# all-reduce only makes progress once all of its CTAs are resident: measured on
-# 8xB200, 2 ranks overlap fully with 16 free SMs (exposed 0.33 -> 0.003 ms), 4 and
-# 8 ranks (32 channels) need 32 (8 ranks: exposed 0.60 -> 0.18 ms; 24 or 28 free SMs
-# change nothing).  FSW_COMM_SMS overrides; 0 disables the cap.
+# kernels only make progress once ALL of their CTAs are resident, so the number of
+# free SMs must cover the CTAs NCCL launches: a group made by new_collective_group()
+# caps them (NCCL config max_ctas) and exactly that many SMs are reserved; for any
+# other group 16 SMs (2 ranks) or 32 (more; NCCL's default channel count there) are.
+# FSW_COMM_SMS overrides; 0 disables the cap.
 _COMM_SMS_ENV = os.environ.get("FSW_COMM_SMS")
+_GROUP_MAX_CTAS = {}  # process group -> CTA cap it was created with
+DEFAULT_COLLECTIVE_CTAS = 16
 
 
-def comm_sms(world_size: int) -> int:
+def new_collective_group(ranks=None, max_ctas: int = DEFAULT_COLLECTIVE_CTAS, **kwargs):
+    """A process group for the dX collective whose NCCL kernels launch at most
+    ``max_ctas`` CTAs, so that they fit into the SMs the dW GEMM leaves free beside
+    them (pass it as ``group=``).  On a non-NCCL backend this is a plain new_group."""
+    if dist.get_backend() != "nccl":
+        return dist.new_group(ranks, **kwargs)
+    opts = dist.ProcessGroupNCCL.Options()
+    opts.config.max_ctas = int(max_ctas)
+    opts.config.min_ctas = min(int(max_ctas), 4)
+    group = dist.new_group(ranks, pg_options=opts, **kwargs)
+    _GROUP_MAX_CTAS[group] = int(max_ctas)
+    return group
+
+
+def comm_sms(world_size: int, group=None) -> int:
     if _COMM_SMS_ENV is not None:
         return int(_COMM_SMS_ENV)
+    if group is not None and group in _GROUP_MAX_CTAS:
+        return _GROUP_MAX_CTAS[group]
     return 16 if world_size <= 2 else 32
 
 
-# Planning figures for the part of the dW GEMM that runs beside the all-reduce of dX:
-# the bus bandwidth NCCL reaches through NVSwitch while confined to comm_sms() SMs beside a
-# GEMM (measured on 8xB200 from the exposed time of a 268 MB and a 1.07 GB all-reduce:
-# ~215 GB/s on 2 ranks, ~225 on 4, ~490 on 8, where the switch reduces), its fixed
-# cost, and the sustained rate of the GEMM on the full GPU.
+# Duration of the dX collective, measured once per (group, message, kind) on the
+# first backward that needs it (two timed runs on a scratch tensor, synchronously -
+# like an autotuner's first call) and used from then on to size the part of the dW
+# GEMM that runs beside it.  Without a CUDA tensor (CPU tests) the planning figures
+# below are used instead.
+_COLLECTIVE_SECONDS = {}
+
+
+def collective_seconds(dx: torch.Tensor, group, collective: str) -> Optional[float]:
+    if not dx.is_cuda:
+        return None
+    key = (group, dx.numel() * dx.element_size(), collective)
+    if key not in _COLLECTIVE_SECONDS:
+        world = dist.get_world_size(group)
+        src = torch.zeros_like(dx)
+        dst = torch.empty((dx.shape[0] // world, dx.shape[1]), device=dx.device, dtype=dx.dtype) \
+            if collective == "reduce_scatter" else None
+        best = None
+        for i in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            if dst is not None:
+                dist.reduce_scatter_tensor(dst, src, group=group)
+            else:
+                dist.all_reduce(src, group=group)
+            e1.record()
+            e1.synchronize()
+            if i > 0:
+                t = e0.elapsed_time(e1) * 1e-3
+                best = t if best is None else min(best, t)
+        _COLLECTIVE_SECONDS[key] = best
+    return _COLLECTIVE_SECONDS[key]
+
+
+# Planning figures used when the collective has not been measured (see
+# collective_seconds): the bus bandwidth NCCL reaches through NVSwitch while confined
+# to a few SMs beside a GEMM, its fixed cost, and the sustained rate of the GEMM on
+# the full GPU.
 ALLREDUCE_BUS_BYTES_PER_S = {2: 215e9, 4: 225e9, 8: 490e9}
 ALLREDUCE_BUS_BYTES_PER_S_OTHER = 225e9
 ALLREDUCE_FIXED_S = 40e-6
@@ -62,18 +114,23 @@ DW_SPLIT_ALIGN = 256  # columns per dW tile
 
 
 def plan_dw_split(T: int, dm: int, di_local: int, world_size: int, sm_count: int, reserve: int,
-                  elem_bytes: int = 2, collective: str = "all_reduce") -> int:
+                  elem_bytes: int = 2, collective: str = "all_reduce",
+                  measured_seconds: Optional[float] = None) -> int:
     """Columns of the local dW GEMM to run on ``sm_count - reserve`` SMs beside the
     collective on dX (T x dm elements; ``"all_reduce"`` or ``"reduce_scatter"``, which
     moves half the bytes); the remaining columns run afterwards on all SMs.  The
     first part is sized to last 1.1x the estimated collective time; returns
-    ``di_local`` when the whole GEMM is needed to cover it."""
+    ``di_local`` when the whole GEMM is needed to cover it.  ``measured_seconds`` is the
+    collective's measured duration, if known; otherwise it is estimated."""
     if world_size <= 1 or reserve <= 0:
         return 0
-    bus = ALLREDUCE_BUS_BYTES_PER_S.get(world_size, ALLREDUCE_BUS_BYTES_PER_S_OTHER)
-    passes = 2.0 if collective == "all_reduce" else 1.0
-    t_ar = passes * (world_size - 1) / world_size * T * dm * elem_bytes / bus
-    t_ar += ALLREDUCE_FIXED_S
+    if measured_seconds is not None:
+        t_ar = measured_seconds
+    else:
+        bus = ALLREDUCE_BUS_BYTES_PER_S.get(world_size, ALLREDUCE_BUS_BYTES_PER_S_OTHER)
+        passes = 2.0 if collective == "all_reduce" else 1.0
+        t_ar = passes * (world_size - 1) / world_size * T * dm * elem_bytes / bus
+        t_ar += ALLREDUCE_FIXED_S
     rate = GEMM_SUSTAINED_FLOPS * max(1, sm_count - reserve) / sm_count
     t_dw = 4.0 * T * dm * di_local / rate
     cols = int(di_local * min(1.0, 1.1 * t_ar / t_dw))
@@ -123,7 +180,7 @@ class _CudaBackend:
 
     @staticmethod
     def grad_weights_beside_collective(x2d, dg, du, *, fast_accum=False, world_size=2, work=None,
-                                       collective="all_reduce"):
+                                       collective="all_reduce", group=None, collective_s=None):
         """dW GEMM while the collective on dX (``work``) is in flight.
 
         NCCL's kernel makes no progress until all of its CTAs are resident, so the
@@ -131,14 +188,15 @@ class _CudaBackend:
         the GEMM is longer than the collective, only a first column range sized to
         the collective's estimated duration runs that way; the current stream then
         waits for the collective and the remaining columns get the whole GPU."""
-        reserve = comm_sms(world_size)
+        reserve = comm_sms(world_size, group)
         if reserve <= 0:
             return _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum)
         with torch.cuda.device(x2d.device) if x2d.is_cuda else contextlib.nullcontext():
             sms = _lib.get_option("sm_count")  # of the device the tensors live on
         T, dm = x2d.shape
         di = dg.shape[1]
-        first = (plan_dw_split(T, dm, di, world_size, sms, reserve, x2d.element_size(), collective)
+        first = (plan_dw_split(T, dm, di, world_size, sms, reserve, x2d.element_size(), collective,
+                               collective_s)
                  if work is not None else di)
         cap = max(2, sms - reserve)  # an argument of this one launch, not process-wide state
         if first >= di:
@@ -203,12 +261,14 @@ class ColumnParallelSwiGLU(Function):
         dg, du = backend.gate_grad(dout, g, u)
         dx = backend.grad_input(dg, du, wg, wu)
         work = None
+        kind = "reduce_scatter" if sharded else "all_reduce"
         if dist.is_initialized() and dist.get_world_size(group) > 1:
+            seconds = collective_seconds(dx, group, kind)  # measured on first use, then cached
             work, dx = _reduce_dx(dx, group, sharded)
         if work is not None and hasattr(backend, "grad_weights_beside_collective"):
             dwg, dwu = backend.grad_weights_beside_collective(
                 x2d, dg, du, fast_accum=fast_accum, world_size=dist.get_world_size(group), work=work,
-                collective="reduce_scatter" if sharded else "all_reduce")
+                collective=kind, group=group, collective_s=seconds)
         else:
             dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=fast_accum)
         if work is not None:
@@ -263,10 +323,12 @@ class TensorParallelSwiGLUMLP(Function):
         dx = backend.grad_input(dg, du, wg, wu)
         work = None
         if dist.is_initialized() and dist.get_world_size(group) > 1:
+            seconds = collective_seconds(dx, group, "all_reduce")
             work = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group, async_op=True)
         if work is not None and hasattr(backend, "grad_weights_beside_collective"):
             dwg, dwu = backend.grad_weights_beside_collective(
-                x2d, dg, du, fast_accum=False, world_size=dist.get_world_size(group), work=work)
+                x2d, dg, du, fast_accum=False, world_size=dist.get_world_size(group), work=work,
+                group=group, collective_s=seconds)
         else:
             dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=False)
         if work is not None:
