@@ -36,6 +36,23 @@ def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+_WORKSPACE_BYTES = {}
+
+
+def _workspace(t: torch.Tensor) -> Optional[torch.Tensor]:
+    """Scratch for the split of a GEMM's last wave of tiles along K (see
+    fsw_workspace_bytes in the header).  Allocated per call from torch's caching
+    allocator, which keeps reuse stream-ordered; the library itself allocates nothing."""
+    dev = t.device.index
+    if dev not in _WORKSPACE_BYTES:
+        with torch.cuda.device(t.device):
+            n = int(_lib.load().fsw_workspace_bytes())
+        if n < 0:
+            _lib.check("fsw_workspace_bytes", n)
+        _WORKSPACE_BYTES[dev] = n
+    return torch.empty(_WORKSPACE_BYTES[dev], device=t.device, dtype=torch.uint8)
+
+
 def forward(
     x2d: torch.Tensor,
     w_gate: torch.Tensor,
@@ -77,32 +94,38 @@ def gate_grad(dout: torch.Tensor, g: torch.Tensor, u: torch.Tensor) -> Tuple[tor
     return dg, du
 
 
-def grad_input(dg: torch.Tensor, du: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
-    """dX (T, dm) = dg @ w_gate^T + du @ w_up^T, accumulated in fp32 in one GEMM."""
+def grad_input(dg: torch.Tensor, du: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *,
+               split_k: bool = True) -> torch.Tensor:
+    """dX (T, dm) = dg @ w_gate^T + du @ w_up^T, accumulated in fp32 in one GEMM.
+    ``split_k`` lets the last partial wave of tiles be divided along K (needs scratch)."""
     _require_cuda(dg, du, w_gate, w_up)
     T, di = dg.shape
     dm = w_gate.shape[0]
     dx = torch.empty((T, dm), device=dg.device, dtype=dg.dtype)
+    ws = _workspace(dg) if split_k and T > 0 else None
     with torch.cuda.device(dg.device):
-        rc = _lib.load().fsw_backward_dx(
+        rc = _lib.load().fsw_backward_dx_ws(
             dg.data_ptr(), du.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), dx.data_ptr(),
-            T, dm, di, _code(dg), _lib.FSW_ACC_F32, _stream(dg),
+            T, dm, di, ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+            _code(dg), _lib.FSW_ACC_F32, _stream(dg),
         )
-    _lib.check("fsw_backward_dx", rc)
+    _lib.check("fsw_backward_dx_ws", rc)
     return dx
 
 
 def grad_weights(
     x2d: torch.Tensor, dg: torch.Tensor, du: torch.Tensor, *, fast_accum: bool = False,
     out_gate: Optional[torch.Tensor] = None, out_up: Optional[torch.Tensor] = None,
-    columns: Optional[Tuple[int, int]] = None, max_sms: int = 0,
+    columns: Optional[Tuple[int, int]] = None, max_sms: int = 0, split_k: bool = True,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """(dW_gate, dW_up), each (dm, di), reduced over all T rows of x2d.
 
     ``columns=(first, count)`` computes only that column range of both gradients
     (the rest of the output tensors is left as it is); pass ``out_gate``/``out_up``
     to collect several ranges in one pair of tensors.  ``max_sms`` > 0 caps the SMs
-    this launch occupies (to leave room for a kernel that runs beside it)."""
+    this launch occupies (to leave room for a kernel that runs beside it).  ``split_k``
+    lets the last partial wave of tiles be divided along the token dimension over all
+    SMs (needs scratch; the sum is then associated differently in those tiles)."""
     _require_cuda(x2d, dg, du)
     T, dm = x2d.shape
     di = dg.shape[1]
@@ -110,7 +133,8 @@ def grad_weights(
     dwu = out_up if out_up is not None else torch.empty((dm, di), device=x2d.device, dtype=x2d.dtype)
     acc = _lib.FSW_ACC_F16 if fast_accum else _lib.FSW_ACC_F32
     with torch.cuda.device(x2d.device):
-        if columns is None and max_sms > 0:
+        ws = _workspace(x2d) if split_k and T > 0 else None
+        if columns is None and (max_sms > 0 or ws is not None):
             columns = (0, di)
         if columns is None:
             name = "fsw_backward_dw"
@@ -122,7 +146,9 @@ def grad_weights(
             name = "fsw_backward_dw_columns"
             rc = _lib.load().fsw_backward_dw_columns(
                 x2d.data_ptr(), dg.data_ptr(), du.data_ptr(), dwg.data_ptr(), dwu.data_ptr(),
-                T, dm, di, int(columns[0]), int(columns[1]), int(max_sms), _code(x2d), acc, _stream(x2d),
+                T, dm, di, int(columns[0]), int(columns[1]), int(max_sms),
+                ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                _code(x2d), acc, _stream(x2d),
             )
     _lib.check(name, rc)
     return dwg, dwu

@@ -21,10 +21,13 @@ SIGNATURES = {
     "fsw_backward_elementwise": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_void_p]),
     "fsw_backward_dx": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_backward_dw": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
-    "fsw_backward_dw_columns": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_int, c_int, c_int, c_void_p]),
+    "fsw_backward_dw_columns": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_int, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "fsw_backward_dx_ws": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "fsw_workspace_bytes": (c_int64, []),
     "fsw_backward": (c_int, [c_void_p] * 11 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_gemm": (c_int, [c_void_p] * 3 + [c_int64] * 3 + [c_int] * 4 + [c_void_p]),
     "fsw_backward_static_scratch": (c_int, [c_void_p] * 9 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
+    "fsw_debug_split_work": (c_int, [c_int] * 7 + [POINTER(c_int64), POINTER(c_int)]),
     "fsw_debug_decode_tile": (c_int, [c_int] * 4 + [POINTER(c_int), POINTER(c_int)]),
     "fsw_debug_descriptors": (c_int, [c_int] * 6 + [POINTER(c_uint32), POINTER(c_uint64), POINTER(c_uint64)]),
     "fsw_last_error": (c_char_p, []),

@@ -56,6 +56,7 @@ struct Options {
                                  // the two dies keep sharing operand panels in L2 (0 = off)
   int64_t pace_limit_us = 50;    // longest wait at one meeting point
   int64_t ew_blocks_per_sm = 32;  // grid cap of the elementwise kernel, per SM
+  int64_t split_k = 1;            // 0: never split the last wave of tiles along K
 };
 static Options g_opt;
 
@@ -370,7 +371,7 @@ static int sm_budget(const DeviceInfo* d, int max_sms) {
 }
 
 static TileChoice choose_tiles(int mode, int64_t rows, int64_t cols, const DeviceInfo* d,
-                               int max_sms = 0) {
+                               int max_sms = 0, bool can_split = false) {
   const int want_cg = (int)g_opt.cta_group, want_ns = (int)g_opt.nsub;
   const int region_n = (mode == MODE_FWD || mode == MODE_DW) ? 128 : 256;
   const struct {
@@ -389,7 +390,10 @@ static TileChoice choose_tiles(int mode, int64_t rows, int64_t cols, const Devic
     }
     const double tiles = (double)((rows + 128 * c.cg - 1) / (128 * c.cg)) *
                          (double)((cols + region_n * c.nsub - 1) / (region_n * c.nsub));
-    const double waves = (double)(int64_t)((tiles + workers - 1) / workers);
+    double waves = (double)(int64_t)((tiles + workers - 1) / workers);
+    // With a workspace the 256x512 configuration splits its last partial wave along K
+    // over all workers, so it loses (almost) nothing to a ragged tile count.
+    if (can_split && c.cg == 2 && c.nsub == 2 && tiles > workers / 4) waves = tiles / workers + 0.05;
     const double score = c.speed * tiles / (waves * workers);
     if (score > best_score) {
       best_score = score;
@@ -399,9 +403,33 @@ static TileChoice choose_tiles(int mode, int64_t rows, int64_t cols, const Devic
   return best;
 }
 
+// Plan of the split of the last partial wave along K for `tiles` tiles of `ipt` K
+// iterations each on `pairs` CTA pairs: true if it pays.  Costs beyond the pieces'
+// own iterations: one more (short) kernel and a round trip of the pieces through
+// the workspace, put at 25 K iterations plus 0.3 per piece.
+static bool plan_split(long long tiles, int pairs, long long ipt, int* first_tile, int* share,
+                       long long* total) {
+  const long long whole = (tiles / pairs) * pairs;
+  const long long rem = tiles - whole;
+  if (rem <= 0) return false;
+  const long long tot = rem * ipt;
+  const long long sh = (tot + pairs - 1) / pairs;
+  const double cost = (double)sh + 25.0 + 0.3 * (double)(pairs + rem);
+  if (!(cost < 0.9 * (double)ipt) || sh < 1 || tot >= (1ll << 40)) return false;
+  *first_tile = (int)whole;
+  *share = (int)sh;
+  *total = tot;
+  return true;
+}
+
+static int64_t splitk_workspace_bytes(const DeviceInfo* d) {
+  return (int64_t)d->max_pairs * 2 * kSplitSlotFloats * (int64_t)sizeof(float);
+}
+
 template <int MODE>
 static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t st,
-                    DeviceInfo* d, TileChoice tc, int max_sms = 0) {
+                    DeviceInfo* d, TileChoice tc, int max_sms = 0, void* ws = nullptr,
+                    int64_t ws_bytes = 0) {
   const int cg = tc.cg;
   const int nsub = tc.nsub;
   const int tile_m = 128 * cg;
@@ -484,9 +512,37 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   if (cg == 2) {
     int max_pairs = d->max_pairs < avail_sms / 2 ? d->max_pairs : avail_sms / 2;
     if (max_pairs < 1) max_pairs = 1;
-    const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
+    int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
+    // Split the last partial wave along K over all pairs when the caller gave a
+    // workspace and the tail would otherwise idle most of the GPU.
+    constexpr int nseg = (MODE == MODE_DX) ? 2 : 1;
+    const long long ipt = (long long)nseg * p.num_k_blocks;
+    p.sk_total_iters = 0;
+    if (MODE != MODE_FWD && nsub == 2 && ws != nullptr && g_opt.split_k != 0 &&
+        ws_bytes >= (int64_t)max_pairs * 2 * kSplitSlotFloats * (int64_t)sizeof(float) &&
+        (reinterpret_cast<uintptr_t>(ws) & 15u) == 0) {
+      if (plan_split(tiles, max_pairs, ipt, &p.sk_first_tile, &p.sk_iters_per_cluster,
+                     &p.sk_total_iters)) {
+        p.sk_ws = static_cast<float*>(ws);
+        pairs = max_pairs;
+      }
+    }
     e = (nsub == 2) ? launch_cg<MODE, 2, 2>(p, 2 * pairs, dtype, acc16, st)
                     : launch_cg<MODE, 2, 1>(p, 2 * pairs, dtype, acc16, st);
+    if (e == cudaSuccess && p.sk_total_iters > 0) {
+      const int rem = (int)(tiles - p.sk_first_tile);
+      constexpr bool dual = (MODE == MODE_DW);
+      const float4* w4 = reinterpret_cast<const float4*>(p.sk_ws);
+      if (dtype == FSW_BF16)
+        splitk_reduce_kernel<__nv_bfloat16, dual><<<rem * 16, 256, 0, st>>>(
+            w4, p.c0_ptr, p.c1_ptr, p.M, p.N, p.ldc, p.num_m_tiles, p.num_n_tiles, p.group_m,
+            p.sk_first_tile, (int)ipt, p.sk_iters_per_cluster);
+      else
+        splitk_reduce_kernel<__half, dual><<<rem * 16, 256, 0, st>>>(
+            w4, p.c0_ptr, p.c1_ptr, p.M, p.N, p.ldc, p.num_m_tiles, p.num_n_tiles, p.group_m,
+            p.sk_first_tile, (int)ipt, p.sk_iters_per_cluster);
+      e = cudaGetLastError();
+    }
   } else {
     const int ctas = (int)(tiles < avail_sms ? tiles : avail_sms);
     e = launch_cg<MODE, 1, 1>(p, ctas, dtype, acc16, st);
@@ -675,6 +731,9 @@ int fsw_set_option(const char* name, int64_t value) {
   } else if (!strcmp(name, "l2_promo")) {
     if (value < 0 || value > 2) return fail(FSW_EINVAL, "l2_promo must be 0, 1 or 2");
     g_opt.l2_promo = value;
+  } else if (!strcmp(name, "split_k")) {
+    if (value != 0 && value != 1) return fail(FSW_EINVAL, "split_k must be 0 or 1");
+    g_opt.split_k = value;
   } else if (!strcmp(name, "ew_blocks_per_sm")) {
     if (value < 1 || value > 64) return fail(FSW_EINVAL, "ew_blocks_per_sm must be in [1, 64]");
     g_opt.ew_blocks_per_sm = value;
@@ -690,6 +749,7 @@ int64_t fsw_get_option(const char* name) {
   if (!strcmp(name, "group_m")) return g_opt.group_m;
   if (!strcmp(name, "nsub")) return g_opt.nsub;
   if (!strcmp(name, "ew_blocks_per_sm")) return g_opt.ew_blocks_per_sm;
+  if (!strcmp(name, "split_k")) return g_opt.split_k;
   if (!strcmp(name, "gemm_max_sms")) return g_opt.gemm_max_sms;
   if (!strcmp(name, "wait_limit_ms")) return g_opt.wait_limit_ms;
   if (!strcmp(name, "stall_producer")) return g_opt.stall_producer;
@@ -806,6 +866,12 @@ int fsw_backward_elementwise(const void* dout, const void* g, const void* u, voi
 
 int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const void* w_up, void* dx,
                     int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream) {
+  return fsw_backward_dx_ws(dg, du, w_gate, w_up, dx, T, dm, di, nullptr, 0, dtype, accum, stream);
+}
+
+int fsw_backward_dx_ws(const void* dg, const void* du, const void* w_gate, const void* w_up,
+                       void* dx, int64_t T, int64_t dm, int64_t di, void* workspace,
+                       int64_t workspace_bytes, int dtype, int accum, void* stream) {
   int rc = check_common(T, dm, di, dtype, accum);
   if (rc != FSW_OK) return rc;
   if (T == 0) return FSW_OK;
@@ -814,7 +880,7 @@ int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const vo
     return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
   DeviceInfo* d = nullptr;
   if ((rc = ensure_device(&d)) != FSW_OK) return rc;
-  const TileChoice tc = choose_tiles(MODE_DX, T, dm, d);
+  const TileChoice tc = choose_tiles(MODE_DX, T, dm, d, 0, workspace != nullptr);
   const int cg = tc.cg;
   GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -827,14 +893,15 @@ int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const vo
   p.N = (int)dm;
   p.num_k_blocks = (int)((di + 63) / 64);
   return run_gemm<MODE_DX>(p, (int)T, dtype, accum == FSW_ACC_F16,
-                           static_cast<cudaStream_t>(stream), d, tc);
+                           static_cast<cudaStream_t>(stream), d, tc, 0, workspace, workspace_bytes);
 }
 
 // Columns [col0, col0 + ncols) of both weight gradients; all pointers are to the
 // full arrays, whose rows are di elements long.
 static int backward_dw_columns(const void* x, const void* dg, const void* du, void* dw_gate,
                                void* dw_up, int64_t T, int64_t dm, int64_t di, int64_t col0,
-                               int64_t ncols, int max_sms, int dtype, int accum, void* stream) {
+                               int64_t ncols, int max_sms, void* ws, int64_t ws_bytes, int dtype,
+                               int accum, void* stream) {
   int rc = check_common(T, dm, di, dtype, accum);
   if (rc != FSW_OK) return rc;
   if (max_sms < 0) return fail(FSW_EINVAL, "max_sms must be >= 0 (0 = no cap of its own)");
@@ -874,19 +941,30 @@ static int backward_dw_columns(const void* x, const void* dg, const void* du, vo
   p.ldc = (int)di;
   p.num_k_blocks = (int)((T + 63) / 64);
   return run_gemm<MODE_DW>(p, (int)dm, dtype, accum == FSW_ACC_F16, st, d,
-                           choose_tiles(MODE_DW, dm, ncols, d, max_sms), max_sms);
+                           choose_tiles(MODE_DW, dm, ncols, d, max_sms, ws != nullptr), max_sms, ws,
+                           ws_bytes);
 }
 
 int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate, void* dw_up,
                     int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream) {
-  return backward_dw_columns(x, dg, du, dw_gate, dw_up, T, dm, di, 0, di, 0, dtype, accum, stream);
+  return backward_dw_columns(x, dg, du, dw_gate, dw_up, T, dm, di, 0, di, 0, nullptr, 0, dtype,
+                             accum, stream);
 }
 
 int fsw_backward_dw_columns(const void* x, const void* dg, const void* du, void* dw_gate,
                             void* dw_up, int64_t T, int64_t dm, int64_t di, int64_t col0,
-                            int64_t ncols, int max_sms, int dtype, int accum, void* stream) {
-  return backward_dw_columns(x, dg, du, dw_gate, dw_up, T, dm, di, col0, ncols, max_sms, dtype,
-                             accum, stream);
+                            int64_t ncols, int max_sms, void* workspace, int64_t workspace_bytes,
+                            int dtype, int accum, void* stream) {
+  if (workspace_bytes < 0) return fail(FSW_EINVAL, "workspace_bytes < 0");
+  return backward_dw_columns(x, dg, du, dw_gate, dw_up, T, dm, di, col0, ncols, max_sms, workspace,
+                             workspace_bytes, dtype, accum, stream);
+}
+
+int64_t fsw_workspace_bytes(void) {
+  DeviceInfo* d = nullptr;
+  int rc = ensure_device(&d);
+  if (rc != FSW_OK) return rc;
+  return splitk_workspace_bytes(d);
 }
 
 int fsw_backward(const void* dout, const void* x, const void* w_gate, const void* w_up,
@@ -913,6 +991,44 @@ int fsw_debug_decode_tile(int t, int num_m_tiles, int num_n_tiles, int group_m, 
     return fail(FSW_EINVAL, "bad tile query");
   decode_tile_order(t, num_m_tiles, num_n_tiles, group_m, *m_tile, *n_tile);
   return FSW_OK;
+}
+
+// Host copy of the kernels' work distribution with a split last wave, for tests:
+// the plan for `num_m_tiles x num_n_tiles` tiles of `iters_per_tile` K iterations on
+// `pairs` CTA pairs (returns 1 and fills plan[3] = {first split tile, iterations per
+// pair, total split iterations} if the split pays, else 0), and, with item != NULL,
+// work item `idx` of pair `cluster` under that plan as item[6] = {valid, m_tile,
+// n_tile, it0, it1, slot}.
+int fsw_debug_split_work(int num_m_tiles, int num_n_tiles, int group_m, int iters_per_tile,
+                         int pairs, int cluster, int idx, int64_t* plan, int* item) {
+  if (num_m_tiles < 1 || num_n_tiles < 1 || group_m < 1 || iters_per_tile < 1 || pairs < 1 || !plan)
+    return fail(FSW_EINVAL, "bad split query");
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.num_m_tiles = num_m_tiles;
+  p.num_n_tiles = num_n_tiles;
+  p.group_m = group_m;
+  const long long tiles = (long long)num_m_tiles * num_n_tiles;
+  const bool split = plan_split(tiles, pairs, iters_per_tile, &p.sk_first_tile,
+                                &p.sk_iters_per_cluster, &p.sk_total_iters);
+  if (!split) p.sk_total_iters = 0;
+  plan[0] = p.sk_first_tile;
+  plan[1] = p.sk_iters_per_cluster;
+  plan[2] = p.sk_total_iters;
+  if (item != nullptr) {
+    // without a split the kernel launches min(tiles, pairs) pairs
+    const int clusters = split ? pairs : (int)(tiles < pairs ? tiles : pairs);
+    WorkItem w = {0, 0, 0, 0, -1};
+    const bool ok = cluster >= 0 && cluster < clusters && idx >= 0 &&
+                    next_work(p, iters_per_tile, cluster, clusters, idx, w);
+    item[0] = ok ? 1 : 0;
+    item[1] = w.m_tile;
+    item[2] = w.n_tile;
+    item[3] = w.it0;
+    item[4] = w.it1;
+    item[5] = w.slot;
+  }
+  return split ? 1 : 0;
 }
 
 // The descriptor constants a launch would use, for known-answer tests of the encoders.

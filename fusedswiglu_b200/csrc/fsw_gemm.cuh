@@ -86,7 +86,26 @@ struct GemmParams {
   unsigned int* pace;
   int pace_kb;                     // K blocks between two meeting points
   unsigned int pace_limit_ns;      // longest a producer waits at a meeting point
+  // Split of the last, partial wave of tiles along K (sk_total_iters == 0: none).
+  // Tiles [0, sk_first_tile) - a whole number of waves - are computed one per CTA
+  // pair as usual.  The K iterations of the remaining tiles, taken as one range of
+  // sk_total_iters = tiles_left * iterations_per_tile, are cut into equal shares of
+  // sk_iters_per_cluster; pair c takes [c * share, (c + 1) * share), which touches at
+  // most two tiles, and writes each piece's fp32 accumulators to slot 2 * c + piece
+  // of sk_ws.  splitk_reduce_kernel then adds the pieces of each tile in a fixed order.
+  int sk_first_tile;
+  int sk_iters_per_cluster;
+  long long sk_total_iters;
+  float* sk_ws;
 };
+
+// One piece of work of a CTA pair: K iterations [it0, it1) of tile (m_tile, n_tile).
+// slot < 0: the whole tile, results go to the output arrays; otherwise a partial
+// sum that goes to workspace slot `slot`.
+struct WorkItem {
+  int m_tile, n_tile, it0, it1, slot;
+};
+constexpr int kSplitSlotFloats = 2 * 128 * 512;  // one slot: both CTAs' 128 x 512 accumulators
 
 // Epilogue warps: 4 (one per TMEM lane quadrant) or 8 (two per quadrant).
 #ifndef FSW_EPI_WARPS
@@ -271,6 +290,47 @@ __host__ __device__ __forceinline__ void decode_tile_order(int t, int num_m_tile
 __device__ __forceinline__ void decode_tile(int t, const GemmParams& p, int& m_tile, int& n_tile) {
   decode_tile_order(t, p.num_m_tiles, p.num_n_tiles, p.group_m, m_tile, n_tile);
 }
+
+// The idx-th work item of pair `cluster_id` (false when it has no more).  Every role
+// of both CTAs of the pair walks the same sequence.
+__host__ __device__ __forceinline__ bool next_work(const GemmParams& p, int iters_per_tile,
+                                                   int cluster_id, int num_clusters, int idx,
+                                                   WorkItem& w) {
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int whole = p.sk_total_iters > 0 ? p.sk_first_tile : num_tiles;
+  const int t = cluster_id + idx * num_clusters;
+  if (t < whole) {
+    decode_tile_order(t, p.num_m_tiles, p.num_n_tiles, p.group_m, w.m_tile, w.n_tile);
+    w.it0 = 0;
+    w.it1 = iters_per_tile;
+    w.slot = -1;
+    return true;
+  }
+  if (p.sk_total_iters == 0) return false;
+  const int piece = idx - whole / num_clusters;  // `whole` is a multiple of num_clusters
+  if (piece < 0 || piece > 1) return false;
+  const long long u0 = static_cast<long long>(cluster_id) * p.sk_iters_per_cluster;
+  long long u1 = u0 + p.sk_iters_per_cluster;
+  if (u1 > p.sk_total_iters) u1 = p.sk_total_iters;
+  if (u0 >= u1) return false;
+  const int a = static_cast<int>(u0 / iters_per_tile);  // first tile of the split range this pair touches
+  const long long a_end = static_cast<long long>(a + 1) * iters_per_tile;
+  int tile;
+  if (piece == 0) {
+    tile = a;
+    w.it0 = static_cast<int>(u0 - static_cast<long long>(a) * iters_per_tile);
+    w.it1 = static_cast<int>((u1 < a_end ? u1 : a_end) - static_cast<long long>(a) * iters_per_tile);
+  } else {
+    if (u1 <= a_end) return false;
+    tile = a + 1;
+    w.it0 = 0;
+    w.it1 = static_cast<int>(u1 - a_end);
+  }
+  decode_tile_order(p.sk_first_tile + tile, p.num_m_tiles, p.num_n_tiles, p.group_m, w.m_tile, w.n_tile);
+  w.slot = 2 * cluster_id + piece;
+  return true;
+}
+
 
 // ---------------------------------------------------------------- epilogue --
 // tcgen05.ld hands every thread 32 consecutive columns of ONE accumulator row, so
@@ -486,6 +546,41 @@ __device__ __forceinline__ void drain_plain(const GemmParams& p, const EpiCtx& e
   }
 }
 
+// Split-K piece: copy one 256-column accumulator region, as fp32, to the piece's
+// workspace slot.  The slot is laid out in the order tensor memory is read - for
+// every (CTA, lane quadrant, region, 16-column chunk) four float4 vectors per lane,
+// lanes adjacent - so each store instruction of a warp writes 512 contiguous bytes.
+// splitk_reduce_kernel reads the same layout.
+__device__ __forceinline__ size_t splitk_vec_index(int slot, int cta, int q, int r, int c, int j,
+                                                   int lane) {
+  return ((((((static_cast<size_t>(slot) * 2 + cta) * 4 + q) * 2 + r) * 16 + c) * 4 + j) * 32) + lane;
+}
+template <bool ACC16, class Release>
+__device__ __forceinline__ void drain_partial(const GemmParams& p, int lane, uint32_t taddr, int slot,
+                                              int cta, int q, int r, int c_begin, int c_count,
+                                              Release release) {
+  float4* ws = reinterpret_cast<float4*>(p.sk_ws);
+#pragma unroll 1
+  for (int c = c_begin; c < c_begin + c_count; ++c) {
+    uint32_t v[16];
+    ptx::tmem_ld_32x16(taddr + c * 16, v);
+    ptx::tmem_ld_wait();
+    if (c == c_begin + c_count - 1) release();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (ACC16)  // fp16 accumulators sit in the low half of each 32-bit column
+          w[e] = __float_as_uint(__half2float(__ushort_as_half(static_cast<unsigned short>(v[4 * j + e] & 0xFFFFu))));
+        else
+          w[e] = v[4 * j + e];
+      }
+      ptx::st_global_v4(ws + splitk_vec_index(slot, cta, q, r, c, j, lane), w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ kernel --
 template <int MODE, int CG, int NSUB, typename T, bool ACC16>
 __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
@@ -573,21 +668,23 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
       const int kb_per_tile = C::NSEG * num_kb;
       const unsigned int meets_per_tile =
           pacer.on ? static_cast<unsigned int>((kb_per_tile + pacer.kb - 1) / pacer.kb) : 0u;
-      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-        int m_tile, n_tile;
-        decode_tile(t, p, m_tile, n_tile);
-        const int m0 = m_tile * C::TILE_M + cta_rank * C::BM;
-        const int n0 = n_tile * C::TILE_N;
-        // Every wave before this one was full; this one has `in_wave` CTAs.
-        const int wave = (t - cluster_id) / num_clusters;
-        const int left = num_tiles - wave * num_clusters;
+      WorkItem w;
+      for (int idx = 0; ok && next_work(p, kb_per_tile, cluster_id, num_clusters, idx, w); ++idx) {
+        const int m0 = w.m_tile * C::TILE_M + cta_rank * C::BM;
+        const int n0 = w.n_tile * C::TILE_N;
+        // Whole tiles run in waves of num_clusters; every wave before the last is full,
+        // and with a split tail every whole-tile wave is.
+        const bool pace_item = pacer.on && w.slot < 0;
+        const int left = (p.sk_total_iters > 0 ? p.sk_first_tile : num_tiles) - idx * num_clusters;
         const unsigned int in_wave = static_cast<unsigned int>((left < num_clusters ? left : num_clusters) * CG);
-        const unsigned int before = static_cast<unsigned int>(wave) * meets_per_tile * gridDim.x;
+        const unsigned int before = static_cast<unsigned int>(idx) * meets_per_tile * gridDim.x;
         int until_meet = 0;
         unsigned int meet_no = 0;
-        for (int seg = 0; seg < C::NSEG && ok; ++seg) {
-          for (int kb = 0; kb < num_kb; ++kb) {
-            if (pacer.on && --until_meet < 0) {
+        for (int it = w.it0; it < w.it1; ++it) {
+          {
+            const int seg = (C::NSEG == 2 && it >= num_kb) ? 1 : 0;
+            const int kb = it - seg * num_kb;
+            if (pace_item && pacer.on && --until_meet < 0) {
               until_meet = pacer.kb - 1;
               pacer.meet(before + (++meet_no) * in_wave, ctl);
             }
@@ -668,13 +765,14 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
         else
           ptx::mma_commit(bar);
       };
-      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+      WorkItem w;
+      for (int idx = 0; ok && next_work(p, C::NSEG * num_kb, cluster_id, num_clusters, idx, w); ++idx) {
         if (NSUB == 1) {
           ok = bounded_wait_thread(tempty_bar(a), aph ^ 1u, ctl, WAIT_MMA_TMEM_EMPTY);
           if (!ok) break;
           ptx::tc_fence_after_sync();
         }
-        const int iters = C::NSEG * num_kb;
+        const int iters = w.it1 - w.it0;  // a split piece starts its own accumulation at zero
         for (int it = 0; it < iters; ++it) {
           if (FSW_PROFILE) prof_t0 = clock64();
           if (!FSW_DBG_SKIP_LOADS) ok = bounded_wait_thread(full_bar(s), ph, ctl, WAIT_MMA_FULL);
@@ -737,11 +835,10 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
     uint32_t aph = 0;
     bool ok = true;
     long long prof_wait = 0, prof_drain = 0, prof_t0 = 0, prof_tiles = 0;
-    for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
-      int m_tile, n_tile;
-      decode_tile(t, p, m_tile, n_tile);
-      e.row0 = m_tile * C::TILE_M + cta_rank * C::BM + q * 32;
-      const int n0 = n_tile * C::TILE_N;
+    WorkItem w;
+    for (int idx = 0; ok && next_work(p, C::NSEG * num_kb, cluster_id, num_clusters, idx, w); ++idx) {
+      e.row0 = w.m_tile * C::TILE_M + cta_rank * C::BM + q * 32;
+      const int n0 = w.n_tile * C::TILE_N;
       if (FSW_PROFILE) prof_t0 = clock64();
       ok = bounded_wait_warp(tfull_bar(NSUB == 2 ? 0 : a), aph, ctl, WAIT_EPI_TMEM_FULL);
       if (FSW_PROFILE) {
@@ -775,6 +872,8 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
         const bool split = (NSUB == 1 && kSplit == 2);
         if (FSW_DBG_SKIP_EPILOGUE) {
           release();
+        } else if (MODE != MODE_FWD && NSUB == 2 && w.slot >= 0) {
+          drain_partial<ACC16>(p, lane, taddr, w.slot, static_cast<int>(cta_rank), q, r, 0, 16, release);
         } else if (MODE == MODE_FWD) {
           if (split)
             drain_swiglu<C, T, ACC16, 1>(p, e, taddr, rn0, chalf, release);
@@ -828,6 +927,68 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
   if (blockIdx.x == 0 && threadIdx.x == 0 && p.clk_probe != nullptr) {
     p.clk_probe[0] = static_cast<unsigned long long>(clock64() - probe_c0);
     p.clk_probe[1] = ptx::globaltimer_ns() - probe_t0;
+  }
+}
+
+// ------------------------------------------------------ split-K second pass --
+// Adds the fp32 pieces that gemm_kernel left in the workspace for each tile of the
+// split tail (see GemmParams::sk_*) in ascending K order and writes the 16-bit
+// results.  One block per (tile, CTA half, lane quadrant, accumulator region); a warp
+// takes 16-column chunks, lanes are rows, so workspace reads are contiguous.
+template <typename T, bool DUAL>
+__global__ void __launch_bounds__(256)
+    splitk_reduce_kernel(const float4* __restrict__ ws, void* c0, void* c1, int M, int N, int ldc,
+                         int num_m_tiles, int num_n_tiles, int group_m, int first_tile,
+                         int iters_per_tile, int share) {
+  const int b = blockIdx.x;
+  const int r = b & 1, q = (b >> 1) & 3, cta = (b >> 3) & 1, j = b >> 4;
+  const int lane = threadIdx.x & 31, wv = threadIdx.x >> 5;
+  const long long t0 = static_cast<long long>(j) * iters_per_tile;
+  const int c_lo = static_cast<int>(t0 / share);
+  const int c_hi = static_cast<int>((t0 + iters_per_tile - 1) / share);
+  int m_tile, n_tile;
+  decode_tile_order(first_tile + j, num_m_tiles, num_n_tiles, group_m, m_tile, n_tile);
+  const int row = m_tile * 256 + cta * 128 + q * 32 + lane;
+#pragma unroll 1
+  for (int cc = 2 * wv; cc < 2 * wv + 2; ++cc) {
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+    for (int cl = c_lo; cl <= c_hi; ++cl) {
+      const int first = static_cast<int>((static_cast<long long>(cl) * share) / iters_per_tile);
+      const int slot = 2 * cl + (first == j ? 0 : 1);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const float4 f = ws[splitk_vec_index(slot, cta, q, r, cc, v, lane)];
+        acc[4 * v] += f.x;
+        acc[4 * v + 1] += f.y;
+        acc[4 * v + 2] += f.z;
+        acc[4 * v + 3] += f.w;
+      }
+    }
+    // Column of the chunk in the output: a dual region is [128 of c0 | 128 of c1].
+    int col;
+    void* out;
+    if (DUAL) {
+      const int in_region = cc * 16;
+      out = in_region >= 128 ? c1 : c0;
+      col = n_tile * 256 + r * 128 + (in_region & 127);
+    } else {
+      out = c0;
+      col = n_tile * 512 + r * 256 + cc * 16;
+    }
+    if (row < M) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        if (col + 8 * h < N) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) w[e] = pack2<T>(acc[8 * h + 2 * e], acc[8 * h + 2 * e + 1]);
+          ptx::st_global_v4(static_cast<char*>(out) + (static_cast<size_t>(row) * ldc + col + 8 * h) * 2,
+                            w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
   }
 }
 

@@ -67,6 +67,27 @@ int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const vo
                     int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream);
 
 /*
+ * Caller-provided workspace for the GEMMs that can use one (the `_ws` entry points
+ * and fsw_backward_dw_columns).  A GEMM's output tiles rarely fill a whole number
+ * of waves of the GPU's SM pairs; without a workspace the last, partial wave leaves
+ * SMs idle (a quarter of the launch when d_intermediate is split over 8 GPUs).
+ * With one, the K loops of the last wave's tiles are divided evenly over all SM
+ * pairs, the fp32 partial sums go through the workspace, and a short second kernel
+ * adds them in a fixed order (results are deterministic; they can differ from the
+ * no-workspace result in the last bit of those tiles, because the fp32 additions
+ * associate differently).  fsw_workspace_bytes() is the size that suffices for any
+ * launch on the current device (1 MiB per SM pair, 74 MiB on a B200); a smaller,
+ * NULL or misaligned (16 bytes) workspace just means the launch does not split.
+ * The buffer is scratch: its contents mean nothing after the call, and calls that
+ * may overlap on the GPU need different buffers.  Option "split_k" = 0 turns the
+ * splitting off process-wide.  No counterpart in the reference.
+ */
+int64_t fsw_workspace_bytes(void);
+int fsw_backward_dx_ws(const void* dg, const void* du, const void* w_gate, const void* w_up,
+                       void* dx, int64_t T, int64_t dm, int64_t di, void* workspace,
+                       int64_t workspace_bytes, int dtype, int accum, void* stream);
+
+/*
  * Weight gradients: dw_gate = x^T @ dg, dw_up = x^T @ du, reduced over all T
  * tokens in one dual GEMM.  Replaces fused_bmm + bmm_kernel
  * (kernels_bf16.py:280-412, kernels_fp16.py:290-422) and the batch sum
@@ -79,7 +100,8 @@ int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate
  * fsw_backward_dw restricted to columns [col0, col0 + ncols) of dw_gate and dw_up
  * (col0 and ncols multiples of 8).  All pointers are to the FULL arrays: dg and du
  * (T, di), dw_gate and dw_up (dm, di); only the named columns are read and written,
- * and they get exactly the values fsw_backward_dw would give them.  `max_sms` > 0
+ * and, without a workspace, get exactly the values fsw_backward_dw would give them
+ * (`workspace` may be NULL; see fsw_workspace_bytes above).  `max_sms` > 0
  * caps the SMs this one launch occupies (0 = no cap of its own; the process-wide
  * "gemm_max_sms" option, if set, then applies).  Lets a caller cut the
  * weight-gradient GEMM into pieces, e.g. to run one piece beside a collective on
@@ -89,7 +111,8 @@ int fsw_backward_dw(const void* x, const void* dg, const void* du, void* dw_gate
  */
 int fsw_backward_dw_columns(const void* x, const void* dg, const void* du, void* dw_gate,
                             void* dw_up, int64_t T, int64_t dm, int64_t di, int64_t col0,
-                            int64_t ncols, int max_sms, int dtype, int accum, void* stream);
+                            int64_t ncols, int max_sms, void* workspace, int64_t workspace_bytes,
+                            int dtype, int accum, void* stream);
 
 /*
  * Whole backward on one stream: elementwise step into the caller's scratch
@@ -199,6 +222,19 @@ int64_t fsw_get_option(const char* name);
  */
 int fsw_debug_decode_tile(int t, int num_m_tiles, int num_n_tiles, int group_m, int* m_tile,
                           int* n_tile);
+
+/*
+ * Testing aid (host only): the kernels' distribution of work when the last partial
+ * wave of tiles is split along K (see fsw_workspace_bytes).  For a grid of
+ * num_m_tiles x num_n_tiles tiles of iters_per_tile K iterations on `pairs` SM
+ * pairs: returns 1 if the launch would split (0 if not, negative on bad arguments)
+ * and fills plan[3] = {first split tile, K iterations per pair, total split
+ * iterations}; with item != NULL also work item `idx` of pair `cluster` as
+ * item[6] = {valid, m_tile, n_tile, first iteration, end iteration, workspace slot
+ * or -1 for a whole tile}.
+ */
+int fsw_debug_split_work(int num_m_tiles, int num_n_tiles, int group_m, int iters_per_tile,
+                         int pairs, int cluster, int idx, int64_t* plan, int* item);
 
 /*
  * Testing aid (host only): the tcgen05 instruction descriptor for the given types,

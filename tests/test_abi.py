@@ -54,12 +54,12 @@ def test_argument_errors_are_reported_not_raised_across_the_abi():
     rc = lib.fsw_forward(None, None, None, None, None, None, 8, 64, 64, 0, 0, None)
     assert rc == -1 and "required" in _lib.last_error()
     # column range outside the array, or not a multiple of 8
-    rc = lib.fsw_backward_dw_columns(None, None, None, None, None, 8, 64, 64, 32, 40, 0, 0, 0, None)
+    rc = lib.fsw_backward_dw_columns(None, None, None, None, None, 8, 64, 64, 32, 40, 0, None, 0, 0, 0, None)
     assert rc == -1 and "column range" in _lib.last_error()
-    rc = lib.fsw_backward_dw_columns(None, None, None, None, None, 8, 64, 64, 4, 8, 0, 0, 0, None)
+    rc = lib.fsw_backward_dw_columns(None, None, None, None, None, 8, 64, 64, 4, 8, 0, None, 0, 0, 0, None)
     assert rc == -1 and "column range" in _lib.last_error()
     # a negative SM cap
-    rc = lib.fsw_backward_dw_columns(None, None, None, None, None, 8, 64, 64, 0, 8, -1, 0, 0, None)
+    rc = lib.fsw_backward_dw_columns(None, None, None, None, None, 8, 64, 64, 0, 8, -1, None, 0, 0, 0, None)
     assert rc == -1 and "max_sms" in _lib.last_error()
     # misaligned pointer
     rc = lib.fsw_backward_elementwise(8, 16, 16, 16, 16, 64, 0, None)
@@ -133,3 +133,67 @@ def test_descriptor_encoders_known_answers():
     assert sk.value == (1 << 16) | (64 << 32) | (1 << 46) | (2 << 61)
     assert smn.value == (512 << 16) | (64 << 32) | (1 << 46) | (2 << 61)
     assert lib.fsw_debug_descriptors(5, 0, 0, 0, 128, 256, ctypes.byref(idesc), ctypes.byref(sk), ctypes.byref(smn)) == -1
+
+
+def test_split_of_the_last_wave_covers_every_k_iteration_exactly_once():
+    """Host copy of the kernels' work distribution: whole tiles in full waves, then the
+    K iterations of the remaining tiles cut into equal shares, one per SM pair.  Every
+    (tile, K iteration) must be computed exactly once, a pair touches at most two split
+    tiles, slots are unique, and the pieces of a tile are found by the rule the second
+    kernel uses (pair c's first piece belongs to tile floor(c * share / iterations))."""
+    lib = _lib.load()
+    plan = (ctypes.c_int64 * 3)()
+    item = (ctypes.c_int * 6)()
+    cases = [  # (m tiles, n tiles, group_m, K iterations per tile, SM pairs), expect split
+        ((16, 56, 16, 512, 74), True),    # dW of the Llama-3-8B shape: 12 waves + 8 tiles
+        ((16, 7, 16, 512, 74), True),     # its 1/8 column shard: 1 wave + 38 tiles
+        ((16, 7, 2, 512, 66), True),      # the same on 132 SMs: 1 wave + 46 tiles
+        ((16, 7, 2, 512, 58), False),     # on 116 SMs: 1 wave + 54 of 58, nothing to gain
+        ((4, 10, 4, 256, 74), True),      # fewer tiles than pairs
+        ((128, 8, 2, 448, 74), False),    # dX of the same shape: 13 waves + 62 of 74, nothing to gain
+        ((24, 4, 2, 150, 74), True),      # a dX with 1 wave + 22 tiles
+        ((2, 37, 2, 300, 74), False),     # a whole number of waves
+        ((1, 3, 1, 2, 74), False),        # K too short to be worth a second kernel
+        ((3, 5, 2, 1000, 7), True),
+    ]
+    for (nm, nn, gm, ipt, pairs), expect in cases:
+        rc = lib.fsw_debug_split_work(nm, nn, gm, ipt, pairs, 0, 0, plan, None)
+        assert rc == (1 if expect else 0), (nm, nn, ipt, pairs, rc)
+        first_tile, share, total = plan[0], plan[1], plan[2]
+        tiles = nm * nn
+        if expect:
+            assert first_tile % pairs == 0 and 0 < tiles - first_tile < pairs
+            assert total == (tiles - first_tile) * ipt and share * pairs >= total > share * (pairs - 1) - share
+        covered = {}
+        slots = set()
+        order = []
+        for c in range(pairs):
+            pieces = 0
+            for idx in range(tiles // pairs + 4):
+                assert lib.fsw_debug_split_work(nm, nn, gm, ipt, pairs, c, idx, plan, item) >= 0
+                if not item[0]:
+                    continue
+                m, n, it0, it1, slot = item[1], item[2], item[3], item[4], item[5]
+                assert 0 <= m < nm and 0 <= n < nn and 0 <= it0 < it1 <= ipt
+                for it in range(it0, it1):
+                    assert (m, n, it) not in covered, (c, idx, m, n, it)
+                    covered[(m, n, it)] = slot
+                if slot >= 0:
+                    pieces += 1
+                    assert slot not in slots and slot == 2 * c + (pieces - 1)
+                    slots.add(slot)
+                    order.append((m, n, it0, c, slot))
+                else:
+                    assert (it0, it1) == (0, ipt)
+            assert pieces <= 2
+        assert len(covered) == tiles * ipt, (nm, nn, ipt, pairs)
+        # the second kernel's rule for finding the pieces of split tile j, in K order
+        if expect:
+            m_, n_ = ctypes.c_int(), ctypes.c_int()
+            for j in range(tiles - first_tile):
+                lib.fsw_debug_decode_tile(first_tile + j, nm, nn, gm, ctypes.byref(m_), ctypes.byref(n_))
+                c_lo, c_hi = (j * ipt) // share, ((j + 1) * ipt - 1) // share
+                want = [2 * c + (0 if (c * share) // ipt == j else 1) for c in range(c_lo, c_hi + 1)]
+                have = [s for (m, n, it0, c, s) in sorted(order, key=lambda o: (o[0], o[1], o[2]))
+                        if (m, n) == (m_.value, n_.value)]
+                assert have == want, (j, have, want)

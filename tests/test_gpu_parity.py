@@ -203,9 +203,10 @@ def test_tile_and_scheduling_options_do_not_change_results(opts):
     from fusedswiglu_b200 import _lib
 
     inp = orc.make_inputs(1, 1344, 448, 1216, "bf16", seed=21, dout_std=0.5)
-    base = run_cuda(inp, "bf16")
-    old = {k: _lib.get_option(k) for k in opts}
+    old = {k: _lib.get_option(k) for k in list(opts) + ["split_k"]}
     try:
+        _lib.set_option("split_k", 0)  # a split along K adds in another order; it has its own test
+        base = run_cuda(inp, "bf16")
         for k, v in opts.items():
             _lib.set_option(k, v)
         got = run_cuda(inp, "bf16")
@@ -229,9 +230,10 @@ def test_producer_pacing_does_not_change_results(opts):
     from fusedswiglu_b200 import _lib
 
     inp = orc.make_inputs(1, 4224, 512, 2304, "bf16", seed=33, dout_std=0.5)
-    names = sorted(set(opts) | {"pace_kb"})
+    names = sorted(set(opts) | {"pace_kb", "split_k"})
     old = {k: _lib.get_option(k) for k in names}
     try:
+        _lib.set_option("split_k", 0)
         _lib.set_option("pace_kb", 0)
         base = run_cuda(inp, "bf16")
         for k, v in opts.items():
@@ -270,6 +272,50 @@ def test_weight_gradient_column_ranges_equal_the_full_gemm(dtype):
         keep = torch.ones(di, dtype=torch.bool, device=out_g.device)
         keep[sl] = False
         assert bool((out_g[:, keep] == 7.0).all()) and bool((out_u[:, keep] == -3.0).all())
+
+
+@pytest.mark.parametrize("dtype,fast", [("bf16", False), ("fp16", False), ("fp16", True)])
+@pytest.mark.parametrize("T,dm,di", [
+    (16384, 1024, 2560),   # dW: 4 x 10 = 40 tiles on 74 pairs, every pair gets about half a tile
+    (6000, 2048, 4800),    # dW: 8 x 19 = 152 tiles = two whole waves + 4 tiles split 18 ways; dX: 96 tiles
+                           # = one wave + 22 split; ragged T and di
+    (8192, 512, 7176),     # dX: 32 x 1 tiles, K = 2 x 113 blocks; di is not a multiple of 64
+])
+def test_split_of_the_last_wave_along_k(T, dm, di, dtype, fast):
+    """With a workspace the last partial wave of tiles is divided along K over all SM
+    pairs and summed in a second kernel.  Same products, another association of the
+    fp32 sums: the results must agree with the unsplit launch to within a rounding of
+    the output type, and with float64 as closely as the unsplit launch does.  Run
+    twice: the split is deterministic."""
+    from fusedswiglu_b200 import _launch, _lib
+
+    inp = orc.make_inputs(1, T, dm, di, dtype, seed=T + di, dout_std=0.5)
+    x = dev(inp["x"].reshape(T, dm), dtype)
+    wg, wu = dev(inp["w_gate"], dtype), dev(inp["w_up"], dtype)
+    dg = dev(inp["dout"].reshape(T, di), dtype)
+    du = dev((inp["dout"] * 0.5 + 0.125).reshape(T, di), dtype)
+    plain = {"dx": _launch.grad_input(dg, du, wg, wu, split_k=False)}
+    plain["dwg"], plain["dwu"] = _launch.grad_weights(x, dg, du, fast_accum=fast, split_k=False)
+    got = []
+    for _ in range(2):
+        r = {"dx": _launch.grad_input(dg, du, wg, wu)}
+        r["dwg"], r["dwu"] = _launch.grad_weights(x, dg, du, fast_accum=fast)
+        got.append(r)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    ref = {"dx": dg.double() @ wg.double().T + du.double() @ wu.double().T,
+           "dwg": x.double().T @ dg.double(), "dwu": x.double().T @ du.double()}
+    changed = 0
+    for k in plain:
+        assert torch.equal(got[0][k], got[1][k]), k
+        changed += int((got[0][k] != plain[k]).sum())
+        e_split, e_plain = rel_error(got[0][k], ref[k]), rel_error(plain[k], ref[k])
+        print(f"split-K {dtype} fast={fast} T={T} {k}: vs float64 {e_split:.3e} (unsplit {e_plain:.3e}), "
+              f"vs unsplit {rel_error(got[0][k], plain[k]):.3e}")
+        assert e_split < max(1.2 * e_plain, 1e-4), (k, e_split, e_plain)
+        assert rel_error(got[0][k], plain[k]) < (8e-3 if fast else 2e-3), k
+    # the split did run (some last bits differ) unless every partial sum happened to round alike
+    assert changed > 0 or dtype == "fp16"
 
 
 def test_dw_beside_a_collective_in_two_parts_equals_one_launch(monkeypatch):
