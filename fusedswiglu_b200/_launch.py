@@ -60,23 +60,26 @@ def forward(
     *,
     fast_accum: bool = False,
     save_activations: bool = True,
+    split_k: bool = True,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
-    """out, g, u for x2d (T, dm) and weights (dm, di); g and u are None when not saved."""
+    """out, g, u for x2d (T, dm) and weights (dm, di); g and u are None when not saved.
+    ``split_k`` lets the last partial wave of tiles be divided along K (needs scratch)."""
     _require_cuda(x2d, w_gate, w_up)
     T, dm = x2d.shape
     di = w_gate.shape[1]
     out = torch.empty((T, di), device=x2d.device, dtype=x2d.dtype)
     g = torch.empty_like(out) if save_activations else None
     u = torch.empty_like(out) if save_activations else None
+    ws = _workspace(x2d) if split_k and T > 0 else None
     with torch.cuda.device(x2d.device):
-        rc = _lib.load().fsw_forward(
+        rc = _lib.load().fsw_forward_ws(
             x2d.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), out.data_ptr(),
             g.data_ptr() if g is not None else None,
             u.data_ptr() if u is not None else None,
-            T, dm, di, _code(x2d),
-            _lib.FSW_ACC_F16 if fast_accum else _lib.FSW_ACC_F32, _stream(x2d),
+            T, dm, di, ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+            _code(x2d), _lib.FSW_ACC_F16 if fast_accum else _lib.FSW_ACC_F32, _stream(x2d),
         )
-    _lib.check("fsw_forward", rc)
+    _lib.check("fsw_forward_ws", rc)
     return out, g, u
 
 

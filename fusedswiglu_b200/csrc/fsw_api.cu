@@ -406,7 +406,7 @@ static TileChoice choose_tiles(int mode, int64_t rows, int64_t cols, const Devic
 // Plan of the split of the last partial wave along K for `tiles` tiles of `ipt` K
 // iterations each on `pairs` CTA pairs: true if it pays.  Costs beyond the pieces'
 // own iterations: one more (short) kernel and a round trip of the pieces through
-// the workspace, put at 25 K iterations plus 0.3 per piece.
+// the workspace, put at 15 K iterations plus 0.3 per piece.
 static bool plan_split(long long tiles, int pairs, long long ipt, int* first_tile, int* share,
                        long long* total) {
   const long long whole = (tiles / pairs) * pairs;
@@ -414,7 +414,7 @@ static bool plan_split(long long tiles, int pairs, long long ipt, int* first_til
   if (rem <= 0) return false;
   const long long tot = rem * ipt;
   const long long sh = (tot + pairs - 1) / pairs;
-  const double cost = (double)sh + 25.0 + 0.3 * (double)(pairs + rem);
+  const double cost = (double)sh + 15.0 + 0.3 * (double)(pairs + rem);
   if (!(cost < 0.9 * (double)ipt) || sh < 1 || tot >= (1ll << 40)) return false;
   *first_tile = (int)whole;
   *share = (int)sh;
@@ -518,7 +518,7 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
     constexpr int nseg = (MODE == MODE_DX) ? 2 : 1;
     const long long ipt = (long long)nseg * p.num_k_blocks;
     p.sk_total_iters = 0;
-    if (MODE != MODE_FWD && nsub == 2 && ws != nullptr && g_opt.split_k != 0 &&
+    if (nsub == 2 && ws != nullptr && g_opt.split_k != 0 &&
         ws_bytes >= (int64_t)max_pairs * 2 * kSplitSlotFloats * (int64_t)sizeof(float) &&
         (reinterpret_cast<uintptr_t>(ws) & 15u) == 0) {
       if (plan_split(tiles, max_pairs, ipt, &p.sk_first_tile, &p.sk_iters_per_cluster,
@@ -533,7 +533,15 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
       const int rem = (int)(tiles - p.sk_first_tile);
       constexpr bool dual = (MODE == MODE_DW);
       const float4* w4 = reinterpret_cast<const float4*>(p.sk_ws);
-      if (dtype == FSW_BF16)
+      if (MODE == MODE_FWD && dtype == FSW_BF16)
+        splitk_reduce_swiglu_kernel<__nv_bfloat16><<<rem * 16, 256, 0, st>>>(
+            w4, p.store_gu ? p.c0_ptr : nullptr, p.c1_ptr, p.c2_ptr, p.M, p.N, p.num_m_tiles,
+            p.num_n_tiles, p.group_m, p.sk_first_tile, (int)ipt, p.sk_iters_per_cluster);
+      else if (MODE == MODE_FWD)
+        splitk_reduce_swiglu_kernel<__half><<<rem * 16, 256, 0, st>>>(
+            w4, p.store_gu ? p.c0_ptr : nullptr, p.c1_ptr, p.c2_ptr, p.M, p.N, p.num_m_tiles,
+            p.num_n_tiles, p.group_m, p.sk_first_tile, (int)ipt, p.sk_iters_per_cluster);
+      else if (dtype == FSW_BF16)
         splitk_reduce_kernel<__nv_bfloat16, dual><<<rem * 16, 256, 0, st>>>(
             w4, p.c0_ptr, p.c1_ptr, p.M, p.N, p.ldc, p.num_m_tiles, p.num_n_tiles, p.group_m,
             p.sk_first_tile, (int)ipt, p.sk_iters_per_cluster);
@@ -803,6 +811,12 @@ int64_t fsw_get_option(const char* name) {
 
 int fsw_forward(const void* x, const void* w_gate, const void* w_up, void* out, void* g, void* u,
                 int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream) {
+  return fsw_forward_ws(x, w_gate, w_up, out, g, u, T, dm, di, nullptr, 0, dtype, accum, stream);
+}
+
+int fsw_forward_ws(const void* x, const void* w_gate, const void* w_up, void* out, void* g, void* u,
+                   int64_t T, int64_t dm, int64_t di, void* workspace, int64_t workspace_bytes,
+                   int dtype, int accum, void* stream) {
   int rc = check_common(T, dm, di, dtype, accum);
   if (rc != FSW_OK) return rc;
   if (T == 0) return FSW_OK;  // nothing to compute; empty tensors may have NULL storage
@@ -831,7 +845,9 @@ int fsw_forward(const void* x, const void* w_gate, const void* w_up, void* out, 
   p.c1_ptr = u;
   p.c2_ptr = out;
   return run_gemm<MODE_FWD>(p, (int)T, dtype, accum == FSW_ACC_F16,
-                            static_cast<cudaStream_t>(stream), d, choose_tiles(MODE_FWD, T, di, d));
+                            static_cast<cudaStream_t>(stream), d,
+                            choose_tiles(MODE_FWD, T, di, d, 0, workspace != nullptr), 0, workspace,
+                            workspace_bytes);
 }
 
 int fsw_backward_elementwise(const void* dout, const void* g, const void* u, void* dg, void* du,

@@ -872,7 +872,7 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
         const bool split = (NSUB == 1 && kSplit == 2);
         if (FSW_DBG_SKIP_EPILOGUE) {
           release();
-        } else if (MODE != MODE_FWD && NSUB == 2 && w.slot >= 0) {
+        } else if (NSUB == 2 && w.slot >= 0) {
           drain_partial<ACC16>(p, lane, taddr, w.slot, static_cast<int>(cta_rank), q, r, 0, 16, release);
         } else if (MODE == MODE_FWD) {
           if (split)
@@ -989,6 +989,67 @@ __global__ void __launch_bounds__(256)
         }
       }
     }
+  }
+}
+
+// Second pass for the forward: the pieces hold partial sums of [128 gate | 128 up]
+// accumulator regions.  Warp w of a block adds gate chunk w and up chunk w + 8 (the
+// same 16 output columns), rounds g and u to the 16-bit type and applies the same
+// epilogue arithmetic as drain_swiglu: out = round(round(silu_f32(g16)) * u16).
+template <typename T>
+__global__ void __launch_bounds__(256)
+    splitk_reduce_swiglu_kernel(const float4* __restrict__ ws, void* g_out, void* u_out, void* out,
+                                int M, int N, int num_m_tiles, int num_n_tiles, int group_m,
+                                int first_tile, int iters_per_tile, int share) {
+  const int b = blockIdx.x;
+  const int r = b & 1, q = (b >> 1) & 3, cta = (b >> 3) & 1, j = b >> 4;
+  const int lane = threadIdx.x & 31, wv = threadIdx.x >> 5;
+  const long long t0 = static_cast<long long>(j) * iters_per_tile;
+  const int c_lo = static_cast<int>(t0 / share);
+  const int c_hi = static_cast<int>((t0 + iters_per_tile - 1) / share);
+  int m_tile, n_tile;
+  decode_tile_order(first_tile + j, num_m_tiles, num_n_tiles, group_m, m_tile, n_tile);
+  const int row = m_tile * 256 + cta * 128 + q * 32 + lane;
+  const int col = n_tile * 256 + r * 128 + wv * 16;
+  float ag[16], au[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) ag[i] = au[i] = 0.f;
+  for (int cl = c_lo; cl <= c_hi; ++cl) {
+    const int first = static_cast<int>((static_cast<long long>(cl) * share) / iters_per_tile);
+    const int slot = 2 * cl + (first == j ? 0 : 1);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const float4 fg = ws[splitk_vec_index(slot, cta, q, r, wv, v, lane)];
+      const float4 fu = ws[splitk_vec_index(slot, cta, q, r, wv + 8, v, lane)];
+      ag[4 * v] += fg.x;
+      ag[4 * v + 1] += fg.y;
+      ag[4 * v + 2] += fg.z;
+      ag[4 * v + 3] += fg.w;
+      au[4 * v] += fu.x;
+      au[4 * v + 1] += fu.y;
+      au[4 * v + 2] += fu.z;
+      au[4 * v + 3] += fu.w;
+    }
+  }
+  if (row >= M) return;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (col + 8 * h >= N) continue;
+    uint32_t pg[4], pu[4], po[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      pg[e] = pack2<T>(ag[8 * h + 2 * e], ag[8 * h + 2 * e + 1]);
+      pu[e] = pack2<T>(au[8 * h + 2 * e], au[8 * h + 2 * e + 1]);
+      float g0, g1;
+      unpack2<T>(pg[e], g0, g1);
+      po[e] = mul2<T>(pack2<T>(g0 * sigmoid_f32(g0), g1 * sigmoid_f32(g1)), pu[e]);
+    }
+    const size_t off = (static_cast<size_t>(row) * N + col + 8 * h) * 2;
+    if (g_out != nullptr) {
+      ptx::st_global_v4(static_cast<char*>(g_out) + off, pg[0], pg[1], pg[2], pg[3]);
+      ptx::st_global_v4(static_cast<char*>(u_out) + off, pu[0], pu[1], pu[2], pu[3]);
+    }
+    ptx::st_global_v4(static_cast<char*>(out) + off, po[0], po[1], po[2], po[3]);
   }
 }
 

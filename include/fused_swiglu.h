@@ -83,6 +83,9 @@ int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const vo
  * splitting off process-wide.  No counterpart in the reference.
  */
 int64_t fsw_workspace_bytes(void);
+int fsw_forward_ws(const void* x, const void* w_gate, const void* w_up, void* out, void* g, void* u,
+                   int64_t T, int64_t dm, int64_t di, void* workspace, int64_t workspace_bytes,
+                   int dtype, int accum, void* stream);
 int fsw_backward_dx_ws(const void* dg, const void* du, const void* w_gate, const void* w_up,
                        void* dx, int64_t T, int64_t dm, int64_t di, void* workspace,
                        int64_t workspace_bytes, int dtype, int accum, void* stream);

@@ -318,6 +318,42 @@ def test_split_of_the_last_wave_along_k(T, dm, di, dtype, fast):
     assert changed > 0 or dtype == "fp16"
 
 
+@pytest.mark.parametrize("dtype,fast,save", [("bf16", False, True), ("bf16", False, False), ("fp16", True, True)])
+def test_split_of_the_forward_s_last_wave_along_k(dtype, fast, save):
+    """The forward with a workspace: 8 x 11 = 88 tiles are one wave of 74 plus 14 tiles
+    whose K loops (128 blocks) are divided over all SM pairs; the second kernel adds
+    the pieces, rounds g and u and applies the SwiGLU epilogue.  Ragged T and di."""
+    from fusedswiglu_b200 import _launch, _lib
+
+    T, dm, di = 2000, 8192, 2808
+    inp = orc.make_inputs(1, T, dm, di, dtype, seed=77)
+    x, wg, wu = dev(inp["x"].reshape(T, dm), dtype), dev(inp["w_gate"], dtype), dev(inp["w_up"], dtype)
+    plain = _launch.forward(x, wg, wu, fast_accum=fast, save_activations=save, split_k=False)
+    a = _launch.forward(x, wg, wu, fast_accum=fast, save_activations=save)
+    b = _launch.forward(x, wg, wu, fast_accum=fast, save_activations=save)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    g64, u64 = x.double() @ wg.double(), x.double() @ wu.double()
+    ref = (torch.nn.functional.silu(g64) * u64, g64, u64)
+    changed = 0
+    for k, name in enumerate(("out", "g", "u")):
+        if a[k] is None:
+            assert not save and plain[k] is None
+            continue
+        assert torch.equal(a[k], b[k]), name
+        changed += int((a[k] != plain[k]).sum())
+        e_split, e_plain = rel_error(a[k], ref[k]), rel_error(plain[k], ref[k])
+        print(f"forward split-K {dtype} fast={fast} {name}: vs float64 {e_split:.3e} (unsplit {e_plain:.3e})")
+        assert e_split < max(1.2 * e_plain, 1e-4), (name, e_split, e_plain)
+        assert rel_error(a[k], plain[k]) < (8e-3 if fast else 2e-3), name
+    assert changed > 0 or dtype == "fp16"
+    if save:
+        # out is the epilogue applied to the g and u that were written (the GPU's fast
+        # sigmoid may flip a last bit here and there)
+        want = orc.swiglu_from_saved(host(a[1]), host(a[2]), dtype)
+        assert np.mean(orc.to_bits(host(a[0]), dtype) != orc.to_bits(want, dtype)) < 0.01
+
+
 def test_dw_beside_a_collective_in_two_parts_equals_one_launch(monkeypatch):
     """The split the column-parallel backward uses when the dW GEMM outlasts the
     all-reduce: first columns on fewer SMs, wait for the collective, rest on all SMs."""
@@ -649,9 +685,11 @@ def test_full_size_properties(T, dm, di):
     assert torch.equal(dwg2, dwg * 2) and torch.equal(dwu2, dwu * 2)
     del dg2, du2, dx2, dwg2, dwu2
 
-    # permutation equivariance: reversing the tokens reverses the output rows
-    outp, _, _ = _launch.forward(x.flip(0).contiguous(), wg, wu, save_activations=False)
-    assert torch.equal(outp.flip(0), out)
+    # permutation equivariance: reversing the tokens reverses the output rows (without the
+    # split of the last wave, which would add the K pieces of other tiles in another order)
+    out1, _, _ = _launch.forward(x, wg, wu, save_activations=False, split_k=False)
+    outp, _, _ = _launch.forward(x.flip(0).contiguous(), wg, wu, save_activations=False, split_k=False)
+    assert torch.equal(outp.flip(0), out1)
 
 
 # ------------------------------------------------- bounded waits, error path --
