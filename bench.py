@@ -75,6 +75,9 @@ def parse_args():
     ap.add_argument("--comm-ctas", type=int, default=16, metavar="N",
                     help="N>1: CTAs NCCL may use for the dX collective (= SMs the dW GEMM leaves free beside it); "
                          "0 = NCCL's own choice on the default group with the default reservation")
+    ap.add_argument("--dx-collective", default="peer", choices=["peer", "nccl"],
+                    help="N>1: reduce dX with this library's kernels over NVLink peer memory (PeerDxReducer) "
+                         "or with NCCL beside the dW GEMM")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
@@ -417,6 +420,7 @@ def run_ours(args):
     # The dX collective runs on a group whose NCCL kernels are capped to as many CTAs
     # as the dW GEMM leaves SMs free for them.
     group = parallel.new_collective_group(max_ctas=args.comm_ctas) if world > 1 and args.comm_ctas > 0 else None
+    use_peer = world > 1 and args.dx_collective == "peer"
 
     _lib.load()
     for item in args.opt:
@@ -515,6 +519,19 @@ def run_ours(args):
     wgp = wg.clone().requires_grad_(True)
     wup = wu.clone().requires_grad_(True)
 
+    reducer = None
+    if use_peer:
+        real_reducer = parallel.PeerDxReducer(T, dm, tdt, dev, group)
+
+        class MarkedReducer:
+            @staticmethod
+            def reduce(*a, **kw):
+                Marked._mark(2)
+                launches["n"] += 2  # the scattering dX GEMM and the reduction kernel
+                return real_reducer.reduce(*a, **kw)
+
+        reducer = MarkedReducer
+
     def step(marks=None):
         """One forward + backward.  world == 1: the launch sequence of FusedSwiGLU
         (the autograd Function adds nothing on the device).  world > 1: the package's
@@ -531,7 +548,8 @@ def run_ours(args):
         xin = x.detach().requires_grad_(True)
         wgp.grad = wup.grad = None
         Marked.marks = marks
-        out = parallel.column_parallel_swiglu(xin, wgp, wup, group=group, fast_accum=fast, backend=Marked)
+        out = parallel.column_parallel_swiglu(xin, wgp, wup, group=group, fast_accum=fast, backend=Marked,
+                                              reducer=reducer)
         out.backward(dout)
         if marks: marks[5].record()
         Marked.marks = None
@@ -687,7 +705,8 @@ def run_ours(args):
             xin = x_dev[b].detach().requires_grad_(True)
             wgp.grad = wup.grad = None
             if world > 1:
-                out = parallel.column_parallel_swiglu(xin, wgp, wup, group=group, fast_accum=fast, row_sharded=rs)
+                out = parallel.column_parallel_swiglu(xin, wgp, wup, group=group, fast_accum=fast, row_sharded=rs,
+                                                      reducer=real_reducer if use_peer else None)
             elif dtype == "fp16":
                 out = FastAccumFusedSwiGLU.apply(xin, wgp, wup)
             else:
@@ -810,7 +829,13 @@ def run_ours(args):
             tf = gemm_flops_local / ms / 1e9
             kern[n] = {"ms": ms, "achieved": tf, "unit": "TFLOP/s", "bound": "tensor",
                        "frac": tf / peaks["bf16_tflops_sustained"]}
-    if world > 1:
+    if world > 1 and use_peer:
+        kern["dx_gemm"]["note"] = ("includes the reduction: the GEMM's epilogue stores the partial sums into the "
+                                   "owning ranks' buffers over NVLink, a second kernel waits for the peers and adds "
+                                   "the slices")
+        kern["dw_dual_gemm"]["note"] = "runs on all SMs while copy engines gather the reduced row blocks"
+        kern["collective_exposed_after_dw"] = {"ms": tail_ms}
+    elif world > 1:
         kern["dw_dual_gemm"]["note"] = ("runs beside the NCCL all-reduce of dX; first column range on "
                                         f"{_lib.get_option('sm_count') - parallel.comm_sms(world, group)} SMs")
         kern["collective_exposed_after_dw"] = {"ms": tail_ms}
@@ -846,11 +871,13 @@ def run_ours(args):
         "config": {"workload": args.workload, "bs": bs, "sq": sq, "d_model": dm, "d_intermediate": di,
                    "parallelism": f"column-parallel d_intermediate x{world}" if world > 1 else "single GPU",
                    "timed_path": ("column_parallel_swiglu forward + backward (the package's multi-GPU API), "
-                                  "x replicated, dX all-reduced" if world > 1 else
+                                  "x replicated, dX all-reduced " +
+                                  ("by the library's own kernels over NVLink peer memory (PeerDxReducer)" if use_peer
+                                   else "with NCCL beside the dW GEMM") if world > 1 else
                                   "the four launches of FusedSwiGLU forward + backward"),
                    "l2": "inputs larger than L2 (activations and weights exceed 126 MB); no flush",
                    "preheat_s": args.preheat, "preheat_steps": pre_steps,
-                   "comm_sms_reserved_during_dw": parallel.comm_sms(world, group) if world > 1 else 0,
+                   "comm_sms_reserved_during_dw": parallel.comm_sms(world, group) if world > 1 and not use_peer else 0,
                    "dw_columns_beside_collective": dw_split["first"], "dw_columns_local": di_local,
                    "collective_ms_measured_alone": dw_split["collective_ms"],
                    "accumulate": "fp16 accumulator in forward and dW, fp32 in dX" if fast else "fp32",
@@ -861,7 +888,7 @@ def run_ours(args):
         "frac_of_measured_sustained": value / (peaks["bf16_tflops_sustained"] * world),
         "ms_x_sm_mhz": ms_per_step * sm_mhz if sm_mhz else None,
         "fwd_tokens_per_s": fwd_tokens_per_s,
-        "gpu_launches": n_launches,
+        "gpu_launches": n_launches * world,
         "clocks": clocks,
         "parity": parity,
         "roofline": roofline,

@@ -175,3 +175,45 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         )
     _lib.check("fsw_gemm", rc)
     return c
+
+
+def _ptr_array(ptrs):
+    import ctypes
+
+    return (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+
+
+def grad_input_scatter(dg: torch.Tensor, du: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+                       recv_ptrs, world: int, rank: int) -> None:
+    """The dX GEMM of one rank of a column-parallel group; its epilogue stores the
+    partial sums into the owning ranks' receive buffers (``recv_ptrs``: one device
+    pointer per rank, peer memory mapped into this process; see fsw_backward_dx_scatter)."""
+    _require_cuda(dg, du, w_gate, w_up)
+    T, di = dg.shape
+    dm = w_gate.shape[0]
+    with torch.cuda.device(dg.device):
+        rc = _lib.load().fsw_backward_dx_scatter(
+            dg.data_ptr(), du.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), _ptr_array(recv_ptrs),
+            int(world), int(rank), T, dm, di, _code(dg), _lib.FSW_ACC_F32, _stream(dg),
+        )
+    _lib.check("fsw_backward_dx_scatter", rc)
+
+
+def reduce_dx_slices(recv_ptr: int, peer_flag_ptrs, my_flags_ptr: int, world: int, rank: int, seq: int,
+                     out: torch.Tensor) -> None:
+    """Signal the peers, wait (bounded) for their partials and sum the ``world`` slices
+    of this rank's receive buffer into ``out`` (rows, dm); see fsw_dx_reduce."""
+    rows, dm = out.shape
+    with torch.cuda.device(out.device):
+        rc = _lib.load().fsw_dx_reduce(
+            recv_ptr, _ptr_array(peer_flag_ptrs), my_flags_ptr, int(world), int(rank), int(seq) & 0xFFFFFFFF,
+            rows, dm, out.data_ptr(), _code(out), _stream(out),
+        )
+    _lib.check("fsw_dx_reduce", rc)
+
+
+def wait_flags(flags_ptr: int, n: int, seq: int, like: torch.Tensor) -> None:
+    """Queue a time-limited wait until ``n`` 32-bit flag words have reached ``seq``."""
+    with torch.cuda.device(like.device):
+        rc = _lib.load().fsw_wait_flags(flags_ptr, int(n), int(seq) & 0xFFFFFFFF, _stream(like))
+    _lib.check("fsw_wait_flags", rc)

@@ -912,6 +912,93 @@ int fsw_backward_dx_ws(const void* dg, const void* du, const void* w_gate, const
                            static_cast<cudaStream_t>(stream), d, tc, 0, workspace, workspace_bytes);
 }
 
+// dX GEMM whose epilogue stores the partial sums into the owning ranks' buffers.
+int fsw_backward_dx_scatter(const void* dg, const void* du, const void* w_gate, const void* w_up,
+                            void* const* recv_ptrs, int world, int rank, int64_t T, int64_t dm,
+                            int64_t di, int dtype, int accum, void* stream) {
+  int rc = check_common(T, dm, di, dtype, accum);
+  if (rc != FSW_OK) return rc;
+  if (world < 2 || world > kMaxScatterRanks || rank < 0 || rank >= world)
+    return fail(FSW_EINVAL, "world size %d (2..%d) / rank %d", world, kMaxScatterRanks, rank);
+  if (T <= 0 || T % world != 0 || (T / world) % 32 != 0)
+    return fail(FSW_EINVAL, "T = %lld must split into %d equal parts of a multiple of 32 rows",
+                (long long)T, world);
+  if (!dg || !du || !w_gate || !w_up || !recv_ptrs) return fail(FSW_EINVAL, "NULL pointer");
+  if (!aligned16(dg) || !aligned16(du) || !aligned16(w_gate) || !aligned16(w_up))
+    return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
+  for (int r = 0; r < world; ++r)
+    if (recv_ptrs[r] == nullptr || !aligned16(recv_ptrs[r]))
+      return fail(FSW_EINVAL, "receive buffer of rank %d is NULL or not 16-byte aligned", r);
+  DeviceInfo* d = nullptr;
+  if ((rc = ensure_device(&d)) != FSW_OK) return rc;
+  const TileChoice tc = choose_tiles(MODE_DX, T, dm, d);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  if ((rc = make_map(&p.a0, dg, dtype, di, T, 128, "dg")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.a1, du, dtype, di, T, 128, "du")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.b0, w_gate, dtype, di, dm, 256 / tc.cg, "w_gate")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.b1, w_up, dtype, di, dm, 256 / tc.cg, "w_up")) != FSW_OK) return rc;
+  p.M = (int)T;
+  p.N = (int)dm;
+  p.num_k_blocks = (int)((di + 63) / 64);
+  for (int r = 0; r < world; ++r) p.scatter[r] = recv_ptrs[r];
+  p.scatter_world = world;
+  p.scatter_rank = rank;
+  p.scatter_rows = (int)(T / world);
+  return run_gemm<MODE_DX>(p, (int)T, dtype, accum == FSW_ACC_F16,
+                           static_cast<cudaStream_t>(stream), d, tc);
+}
+
+int fsw_dx_reduce(const void* recv, void* const* peer_flag_ptrs, void* my_flags, int world, int rank,
+                  uint32_t seq, int64_t rows, int64_t dm, void* dx_rows, int dtype, void* stream) {
+  if (dtype != FSW_BF16 && dtype != FSW_FP16) return fail(FSW_EINVAL, "unknown dtype %d", dtype);
+  if (world < 2 || world > kMaxScatterRanks || rank < 0 || rank >= world)
+    return fail(FSW_EINVAL, "world size %d (2..%d) / rank %d", world, kMaxScatterRanks, rank);
+  if (rows <= 0 || dm <= 0 || (dm & 7)) return fail(FSW_EINVAL, "bad shape rows=%lld dm=%lld", (long long)rows, (long long)dm);
+  if (!recv || !peer_flag_ptrs || !my_flags || !dx_rows) return fail(FSW_EINVAL, "NULL pointer");
+  if (!aligned16(recv) || !aligned16(dx_rows) || (reinterpret_cast<uintptr_t>(my_flags) & 3u))
+    return fail(FSW_EINVAL, "pointers must be aligned (16 bytes; flags 4 bytes)");
+  PeerFlags pf;
+  memset(&pf, 0, sizeof(pf));
+  for (int r = 0; r < world; ++r) {
+    if (peer_flag_ptrs[r] == nullptr || (reinterpret_cast<uintptr_t>(peer_flag_ptrs[r]) & 3u))
+      return fail(FSW_EINVAL, "flag pointer of rank %d is NULL or misaligned", r);
+    pf.p[r] = static_cast<unsigned int*>(peer_flag_ptrs[r]);
+  }
+  DeviceInfo* d = nullptr;
+  int rc = ensure_device(&d);
+  if (rc != FSW_OK) return rc;
+  const long long vecs = rows * dm / 8;
+  long long blocks = (vecs + 255) / 256;
+  const long long cap = (long long)d->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned long long limit = (unsigned long long)g_opt.wait_limit_ms * 1000000ull;
+  if (dtype == FSW_BF16)
+    dx_slices_reduce_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const uint4*>(recv), static_cast<__nv_bfloat16*>(dx_rows), vecs, world, rank, seq,
+        pf, static_cast<unsigned int*>(my_flags), d->status, limit);
+  else
+    dx_slices_reduce_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const uint4*>(recv), static_cast<__half*>(dx_rows), vecs, world, rank, seq, pf,
+        static_cast<unsigned int*>(my_flags), d->status, limit);
+  FSW_CUDA(cudaGetLastError());
+  return FSW_OK;
+}
+
+int fsw_wait_flags(void* flags, int n, uint32_t seq, void* stream) {
+  if (!flags || (reinterpret_cast<uintptr_t>(flags) & 3u) || n < 1 || n > 32)
+    return fail(FSW_EINVAL, "bad flag array");
+  DeviceInfo* d = nullptr;
+  int rc = ensure_device(&d);
+  if (rc != FSW_OK) return rc;
+  wait_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<unsigned int*>(flags), n, seq, d->status,
+      (unsigned long long)g_opt.wait_limit_ms * 1000000ull);
+  FSW_CUDA(cudaGetLastError());
+  return FSW_OK;
+}
+
 // Columns [col0, col0 + ncols) of both weight gradients; all pointers are to the
 // full arrays, whose rows are di elements long.
 static int backward_dw_columns(const void* x, const void* dg, const void* du, void* dw_gate,

@@ -97,7 +97,15 @@ struct GemmParams {
   int sk_iters_per_cluster;
   long long sk_total_iters;
   float* sk_ws;
+  // MODE_DX across several GPUs (scatter_world > 1): rows [r * scatter_rows,
+  // (r + 1) * scatter_rows) of dX belong to rank r, and the epilogue stores this
+  // rank's partial sums for them straight into rank r's receive buffer scatter[r]
+  // (peer memory mapped into this process; plain 16-byte stores over NVLink), which
+  // is laid out [source rank][scatter_rows][N].  c0_ptr is not written.
+  void* scatter[8];
+  int scatter_world, scatter_rank, scatter_rows;
 };
+constexpr int kMaxScatterRanks = 8;
 
 // One piece of work of a CTA pair: K iterations [it0, it1) of tile (m_tile, n_tile).
 // slot < 0: the whole tile, results go to the output arrays; otherwise a partial
@@ -539,6 +547,14 @@ __device__ __forceinline__ void drain_plain(const GemmParams& p, const EpiCtx& e
     if (j == NJB - 1) release();
     const int col = (MODE == MODE_DW) ? (n0 + (jb & 1) * 64) : (n0 + jb * 64);
     void* out = (MODE == MODE_DW && jb >= 2) ? p.c1_ptr : p.c0_ptr;
+    if (MODE == MODE_DX && p.scatter_world > 1) {
+      // The warp's 32 rows have one owner (scatter_rows is a multiple of 32).  Row t of
+      // dX is row (rank * scatter_rows + t - owner * scatter_rows) of the owner's buffer.
+      int owner = e.row0 / p.scatter_rows;
+      if (owner >= p.scatter_world) owner = p.scatter_world - 1;  // rows >= M: nothing is stored
+      const long long shift = static_cast<long long>(p.scatter_rank - owner) * p.scatter_rows;
+      out = static_cast<char*>(p.scatter[owner]) + shift * p.ldc * 2;
+    }
     stage_rows128(e.buf, e.lane, pk);
     __syncwarp();
     flush_rows128(e.buf, e.lane, out, e.row0, col, p.M, p.N, p.ldc);
@@ -1050,6 +1066,104 @@ __global__ void __launch_bounds__(256)
       ptx::st_global_v4(static_cast<char*>(u_out) + off, pu[0], pu[1], pu[2], pu[3]);
     }
     ptx::st_global_v4(static_cast<char*>(out) + off, po[0], po[1], po[2], po[3]);
+  }
+}
+
+// ------------------------------------------- reduction of scattered dX partials --
+// Second half of the dX reduce-scatter over NVLink.  Every rank's dX GEMM has stored
+// its partial sums for this rank's rows into slice [source rank] of `recv` (see
+// GemmParams::scatter).  This kernel, launched on the same stream right after that
+// GEMM, (1) tells every peer that this rank's partials are complete - they are: the
+// GEMM kernel has finished - by storing the step number `seq` into the peer's flag
+// word [this rank], (2) waits, with a time limit, until all peers have said the same
+// here, and (3) adds the `world` slices in fp32 in rank order and writes the 16-bit
+// result.  A wait that runs out records WAIT_PEER_PARTIALS in the status word and the
+// block returns without writing (the host reads the status).
+constexpr uint32_t WAIT_PEER_PARTIALS = 5;
+struct PeerFlags {
+  unsigned int* p[kMaxScatterRanks];  // p[r]: rank r's flag words (peer memory)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+    dx_slices_reduce_kernel(const uint4* __restrict__ recv, T* __restrict__ out, long long vecs_per_slice,
+                            int world, int rank, unsigned int seq, const PeerFlags peer_flags,
+                            volatile unsigned int* my_flags, uint32_t* status,
+                            unsigned long long wait_limit_ns) {
+  __shared__ int give_up;
+  if (threadIdx.x == 0) give_up = 0;
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    // the partials were written by an earlier kernel on this stream; order them before
+    // the flag for observers on other GPUs
+    __threadfence_system();
+    unsigned int* f = peer_flags.p[threadIdx.x] + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const uint64_t t0 = ptx::globaltimer_ns();
+    for (;;) {
+      unsigned int v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];"
+                   : "=r"(v)
+                   : "l"(const_cast<unsigned int*>(my_flags) + threadIdx.x)
+                   : "memory");
+      // flags only grow; compare in wrap-around arithmetic
+      if (static_cast<int>(v - seq) >= 0) break;
+      if (ptx::globaltimer_ns() - t0 > wait_limit_ns) {
+        give_up = 1;
+        atomicCAS(status, 0u, WAIT_PEER_PARTIALS | (static_cast<uint32_t>(threadIdx.x) << 8));
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+  if (give_up) return;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < vecs_per_slice;
+       v += stride) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int s = 0; s < world; ++s) {
+      const uint4 w = recv[static_cast<long long>(s) * vecs_per_slice + v];
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float lo, hi;
+        unpack2<T>(ww[e], lo, hi);
+        acc[2 * e] += lo;
+        acc[2 * e + 1] += hi;
+      }
+    }
+    uint4 o;
+    o.x = pack2<T>(acc[0], acc[1]);
+    o.y = pack2<T>(acc[2], acc[3]);
+    o.z = pack2<T>(acc[4], acc[5]);
+    o.w = pack2<T>(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out)[v] = o;
+  }
+}
+
+// Time-limited wait until every word of flags[0..n) has reached `seq`; used to learn
+// that the peers' copies of their reduced rows into this rank's buffer have landed.
+__global__ void wait_flags_kernel(volatile unsigned int* flags, int n, unsigned int seq, uint32_t* status,
+                                  unsigned long long wait_limit_ns) {
+  if (threadIdx.x >= n) return;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  for (;;) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];"
+                 : "=r"(v)
+                 : "l"(const_cast<unsigned int*>(flags) + threadIdx.x)
+                 : "memory");
+    if (static_cast<int>(v - seq) >= 0) return;
+    if (ptx::globaltimer_ns() - t0 > wait_limit_ns) {
+      atomicCAS(status, 0u, WAIT_PEER_PARTIALS | (static_cast<uint32_t>(threadIdx.x) << 8) | 0x80u);
+      return;
+    }
+    __nanosleep(200);
   }
 }
 

@@ -207,6 +207,121 @@ class _CudaBackend:
                                     columns=(first, di - first))
 
 
+class PeerDxReducer:
+    """The dX collective done by this library's own kernels over NVLink peer memory
+    instead of NCCL (pass as ``reducer=`` to column_parallel_swiglu).
+
+    Every rank's dX GEMM stores its partial sums from its epilogue straight into the
+    receive buffer of the rank that owns the rows (reduce-scatter, no extra pass over
+    the partials and no SM taken from a GEMM); a short kernel then waits - with a time
+    limit - for the peers' partials and adds the slices in fp32 in rank order, so the
+    result is deterministic and rounded once.  For the replicated-x mode the reduced
+    row blocks are then copied to every peer by plain device-to-device copies on a side
+    stream (copy engines, no SMs) while the dW GEMM has the whole GPU, and a last
+    time-limited wait confirms that the peers' blocks have landed.
+
+    Buffers live in symmetric memory (torch.distributed._symmetric_memory: the same
+    allocation on every rank, each mapped into every process); only plain loads, stores
+    and copies touch peer memory.  Two sets alternate from step to step: a rank can be
+    one step ahead of a peer, never two, because its reduction waits for every peer's
+    signal of the same step.
+
+    In replicated-x mode the returned dX is a view of an internal buffer that the
+    second-next call overwrites; pass ``own_output=True`` to get a private copy.
+    Collective: construct it on all ranks of ``group`` at the same point."""
+
+    def __init__(self, T: int, dm: int, dtype: torch.dtype, device, group=None, own_output: bool = False):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer access only
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if not 2 <= self.world <= 8:
+            raise ValueError(f"PeerDxReducer serves 2..8 ranks, got {self.world}")
+        if T % self.world or (T // self.world) % 32:
+            raise ValueError(f"T={T} must split into {self.world} equal parts of a multiple of 32 rows")
+        self.T, self.dm, self.dtype, self.device = T, dm, dtype, torch.device(device)
+        self.rows = T // self.world
+        self.own_output = own_output
+        self.seq = 0
+        self.esize = torch.empty((), dtype=dtype).element_size()
+        self.recv = symm_mem.empty(2 * T * dm, dtype=dtype, device=self.device)       # [set][source][rows][dm]
+        self.full = symm_mem.empty(2 * T * dm, dtype=dtype, device=self.device)       # [set][T][dm]
+        self.flags = symm_mem.empty(2 * 2 * self.world, dtype=torch.int32, device=self.device)  # [set][kind][rank]
+        self.flags.zero_()
+        self.h_recv = symm_mem.rendezvous(self.recv, self.group)
+        self.h_full = symm_mem.rendezvous(self.full, self.group)
+        self.h_flags = symm_mem.rendezvous(self.flags, self.group)
+        self.side = torch.cuda.Stream(device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)  # every rank's flags are zero before anyone signals
+
+    # ---- layout of the two buffer sets (host arithmetic; has a CPU test)
+    @staticmethod
+    def layout(seq: int, world: int, rank: int, T: int, dm: int, esize: int) -> dict:
+        """Byte / element offsets used by step ``seq`` (1, 2, ...): which buffer set, where
+        the set's receive slices start, where this rank's row block sits in the gathered
+        dX, and the first flag word of the set's "partials arrived" (kind 0) and "row
+        blocks gathered" (kind 1) arrays."""
+        s = seq & 1
+        rows = T // world
+        return {
+            "set": s,
+            "recv_byte_offset": s * T * dm * esize,           # [set][source rank][rows][dm]
+            "full_elem_offset": s * T * dm,                   # [set][T][dm]
+            "my_block_elem_offset": s * T * dm + rank * rows * dm,
+            "flag_word": {kind: (s * 2 + kind) * world for kind in (0, 1)},  # [set][kind][rank]
+        }
+
+    def _recv_ptrs(self, s):
+        return [p + s * self.T * self.dm * self.esize for p in self.h_recv.buffer_ptrs]
+
+    def _flag_ptrs(self, s, kind):
+        return [p + ((s * 2 + kind) * self.world) * 4 for p in self.h_flags.buffer_ptrs]
+
+    def reduce(self, dg, du, w_gate, w_up, row_sharded: bool):
+        """Queue the scattering dX GEMM and the reduction on the current stream.
+        Returns (dx, finish): call ``finish()`` after queueing the work that should
+        overlap the gather (the dW GEMM); dx is valid on the current stream after it."""
+        self.seq += 1
+        seq, rank, world, rows, dm = self.seq, self.rank, self.world, self.rows, self.dm
+        lay = self.layout(seq, world, rank, self.T, dm, self.esize)
+        s = lay["set"]
+        _launch.grad_input_scatter(dg, du, w_gate, w_up, self._recv_ptrs(s), world, rank)
+        if row_sharded:
+            mine = torch.empty((rows, dm), device=dg.device, dtype=dg.dtype)
+        else:
+            full = self.full[lay["full_elem_offset"]:lay["full_elem_offset"] + self.T * dm].view(self.T, dm)
+            mine = full[rank * rows:(rank + 1) * rows]
+        _launch.reduce_dx_slices(self._recv_ptrs(s)[rank], self._flag_ptrs(s, 0), self._flag_ptrs(s, 0)[rank],
+                                 world, rank, seq, mine)
+        if row_sharded:
+            return mine, (lambda: mine)
+        # gather: my reduced rows to every peer's copy of the full dX, then my step
+        # number into their "gathered" flag word for me - device-to-device copies
+        # queued on a side stream, ordered after the reduction
+        done = torch.cuda.Event()
+        done.record()
+        main = torch.cuda.current_stream(dg.device)
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(done)
+            off = lay["my_block_elem_offset"]
+            for r in range(world):
+                if r != rank:
+                    self.h_full.get_buffer(r, (rows, dm), self.dtype, off).copy_(mine, non_blocking=True)
+            w0, w1 = lay["flag_word"][0] + rank, lay["flag_word"][1] + rank
+            src = self.flags[w0:w0 + 1]  # my own "partials arrived" word: holds seq now
+            for r in range(world):
+                self.h_flags.get_buffer(r, (1,), torch.int32, w1).copy_(src, non_blocking=True)
+
+        def finish():
+            _launch.wait_flags(self._flag_ptrs(s, 1)[rank], world, seq, full)
+            return full.clone() if self.own_output else full
+
+        return full, finish
+
+
 def _reduce_dx(dx, group, row_sharded):
     """Start the one collective of the backward.  Returns (work, result): the
     all-reduce works in place; the reduce-scatter leaves this rank's rows of the
@@ -233,7 +348,7 @@ class ColumnParallelSwiGLU(Function):
 
     @staticmethod
     def forward(ctx, x, w_gate_shard, w_up_shard, group=None, fast_accum=False, backend=None,
-                row_sharded=False):
+                row_sharded=False, reducer=None):
         backend = backend or _CudaBackend
         assert x.ndim == 3 and w_gate_shard.ndim == 2, "Incorrect number of dimensions for LHS or RHS"
         assert w_gate_shard.shape == w_up_shard.shape, "Expected both weight matrices to have same shape"
@@ -250,15 +365,22 @@ class ColumnParallelSwiGLU(Function):
         wu = w_up_shard.contiguous()
         out, g, u = backend.forward(x2d, wg, wu, fast_accum=fast_accum, save_activations=True)
         ctx.save_for_backward(x2d, wg, wu, g, u)
-        ctx.meta = (bs, sq, dm, group, fast_accum, backend, sharded)
+        ctx.meta = (bs, sq, dm, group, fast_accum, backend, sharded, reducer if world > 1 else None)
         return out.view((world if sharded else 1) * bs, sq, wg.shape[1])
 
     @staticmethod
     def backward(ctx, grad_output):
         x2d, wg, wu, g, u = ctx.saved_tensors
-        bs, sq, dm, group, fast_accum, backend, sharded = ctx.meta
+        bs, sq, dm, group, fast_accum, backend, sharded, reducer = ctx.meta
         dout = grad_output.contiguous().view(x2d.shape[0], wg.shape[1])
         dg, du = backend.gate_grad(dout, g, u)
+        if reducer is not None:
+            # this library's own reduce-scatter over peer memory: no NCCL kernel needs
+            # SMs, so the dW GEMM keeps the whole GPU while the row blocks are gathered
+            dx, finish = reducer.reduce(dg, du, wg, wu, sharded)
+            dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=fast_accum)
+            dx = finish()
+            return dx.view(bs, sq, dm), dwg, dwu, None, None, None, None, None
         dx = backend.grad_input(dg, du, wg, wu)
         work = None
         kind = "reduce_scatter" if sharded else "all_reduce"
@@ -273,7 +395,7 @@ class ColumnParallelSwiGLU(Function):
             dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=fast_accum)
         if work is not None:
             work.wait()
-        return dx.view(bs, sq, dm), dwg, dwu, None, None, None, None
+        return dx.view(bs, sq, dm), dwg, dwu, None, None, None, None, None
 
 
 def shard_rows(w: torch.Tensor, rank: int, world_size: int) -> torch.Tensor:
@@ -339,6 +461,9 @@ class TensorParallelSwiGLUMLP(Function):
 def column_parallel_swiglu(
     x: torch.Tensor, w_gate_shard: torch.Tensor, w_up_shard: torch.Tensor,
     group: Optional[dist.ProcessGroup] = None, fast_accum: bool = False, row_sharded: bool = False,
-    backend=None,
+    backend=None, reducer: Optional["PeerDxReducer"] = None,
 ) -> torch.Tensor:
-    return ColumnParallelSwiGLU.apply(x, w_gate_shard, w_up_shard, group, fast_accum, backend, row_sharded)
+    """``reducer``: a PeerDxReducer for this group and (T, d_model): the dX collective is
+    then done by this library's kernels over NVLink peer memory instead of NCCL."""
+    return ColumnParallelSwiGLU.apply(x, w_gate_shard, w_up_shard, group, fast_accum, backend, row_sharded,
+                                      reducer)

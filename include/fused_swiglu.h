@@ -130,6 +130,38 @@ int fsw_backward(const void* dout, const void* x, const void* w_gate, const void
                  int accum, void* stream);
 
 /*
+ * dX reduced across GPUs inside the kernels (no counterpart in the reference, which
+ * is single-GPU).  With d_intermediate split over `world` ranks (2..8) every rank's
+ * dX GEMM yields a partial sum of the whole (T, dm) gradient.  Rank r owns rows
+ * [r*T/world, (r+1)*T/world); T/world must be a multiple of 32.
+ *
+ * fsw_backward_dx_scatter is fsw_backward_dx whose epilogue stores each tile's rows
+ * directly into the owner's receive buffer over NVLink (plain stores to peer memory;
+ * no TMA or multicast touches peer memory): recv_ptrs[r] is rank r's buffer, laid
+ * out [source rank][T/world][dm], mapped into this process (CUDA IPC / symmetric
+ * memory; the caller maps it).  recv_ptrs is a HOST array of `world` device pointers.
+ *
+ * fsw_dx_reduce, called on the same stream right after it, stores `seq` into flag
+ * word [rank] of every rank (peer_flag_ptrs: HOST array of `world` device pointers to
+ * each rank's `world` 32-bit flag words), waits until all `world` words of my_flags
+ * have reached `seq` - i.e. every peer's partials for these rows have arrived - and
+ * writes the fp32 sum of the `world` slices of `recv` (this rank's buffer), rounded
+ * once, to dx_rows (T/world, dm).  `seq` must grow by one per step, and the receive
+ * buffers and flag arrays must alternate between two sets from step to step (a rank
+ * may be one step ahead of a peer, never two).  The wait gives up after
+ * "wait_limit_ms": the kernel then records a code in the status word (fsw_status)
+ * and leaves dx_rows unwritten; nothing hangs.
+ *
+ * fsw_wait_flags waits the same way until flags[0..n) have all reached seq.
+ */
+int fsw_backward_dx_scatter(const void* dg, const void* du, const void* w_gate, const void* w_up,
+                            void* const* recv_ptrs, int world, int rank, int64_t T, int64_t dm,
+                            int64_t di, int dtype, int accum, void* stream);
+int fsw_dx_reduce(const void* recv, void* const* peer_flag_ptrs, void* my_flags, int world, int rank,
+                  uint32_t seq, int64_t rows, int64_t dm, void* dx_rows, int dtype, void* stream);
+int fsw_wait_flags(void* flags, int n, uint32_t seq, void* stream);
+
+/*
  * Plain GEMM on row-major 16-bit arrays with the same tcgen05 kernel:
  *   trans_a = 0, trans_b = 0:  c (M,N) = a (M,K) @ b (K,N)
  *   trans_a = 0, trans_b = 1:  c (M,N) = a (M,K) @ b (N,K)^T

@@ -67,6 +67,33 @@ def _worker(rank, world, port, q):
             "dx_rel": rel(xs_.grad, xr.grad[b0:b1]),
         }
 
+        # the same two modes with the dX collective done by the library's own kernels over
+        # NVLink peer memory (three steps: both buffer sets and their reuse are exercised)
+        reducer = parallel.PeerDxReducer(bs * sq, dm, torch.bfloat16, torch.device("cuda", rank))
+        peer = {}
+        for step in range(3):
+            x3 = x0.clone().requires_grad_(True)
+            wg3 = parallel.shard_columns(wg0, rank, world).requires_grad_(True)
+            wu3 = parallel.shard_columns(wu0, rank, world).requires_grad_(True)
+            o3 = parallel.column_parallel_swiglu(x3, wg3, wu3, reducer=reducer)
+            o3.backward(dout[..., lo:hi].contiguous())
+            x4 = x0[b0:b1].clone().requires_grad_(True)
+            wg4 = parallel.shard_columns(wg0, rank, world).requires_grad_(True)
+            wu4 = parallel.shard_columns(wu0, rank, world).requires_grad_(True)
+            o4 = parallel.column_parallel_swiglu(x4, wg4, wu4, row_sharded=True, reducer=reducer)
+            o4.backward(dout[..., lo:hi].contiguous())
+            torch.cuda.synchronize()
+            peer[step] = {
+                "dx_rel": rel(x3.grad, xr.grad), "dx_rows_rel": rel(x4.grad, xr.grad[b0:b1]),
+                "dx_rows_equal_full": bool(torch.equal(x4.grad, x3.grad[b0:b1])),
+                "dw_equal": bool(torch.equal(wg3.grad, wg.grad) and torch.equal(wu3.grad, wu.grad)
+                                 and torch.equal(wg4.grad, wg.grad) and torch.equal(wu4.grad, wu.grad)),
+            }
+        # every rank holds the same reduced dX
+        gathered = [torch.empty_like(x3.grad) for _ in range(world)]
+        dist.all_gather(gathered, x3.grad.contiguous())
+        peer["same_on_all_ranks"] = all(bool(torch.equal(t, gathered[0])) for t in gathered)
+
         # whole MLP block, tensor parallel vs single GPU
         from fusedswiglu_b200.mlp import FusedSwiGLUMLP
 
@@ -89,6 +116,7 @@ def _worker(rank, world, port, q):
         q.put((rank, {
             "mlp": mlp,
             "row_sharded": row_sharded,
+            "peer": peer,
             "out_equal": bool(torch.equal(out_full, ref.detach())),
             "dwg_equal": bool(torch.equal(wg.grad, wgr.grad[:, lo:hi])),
             "dwu_equal": bool(torch.equal(wu.grad, wur.grad[:, lo:hi])),
@@ -123,6 +151,11 @@ def test_two_gpu_column_parallel_matches_single_gpu():
         rs = r["row_sharded"]
         assert rs["out_equal"] and rs["dwg_equal"] and rs["dwu_equal"] and rs["dx_shape_ok"], (rank, rs)
         assert rs["dx_rel"] < 1e-2, (rank, rs)
+        for step in range(3):
+            pr = r["peer"][step]
+            assert pr["dx_rel"] < 1e-2 and pr["dx_rows_rel"] < 1e-2, (rank, step, pr)
+            assert pr["dx_rows_equal_full"] and pr["dw_equal"], (rank, step, pr)
+        assert r["peer"]["same_on_all_ranks"], rank
         # tensor-parallel MLP: partial sums are rounded per rank before the all-reduce
         for k, v in r["mlp"].items():
             assert v < 1e-2, (rank, k, r["mlp"])

@@ -349,3 +349,35 @@ def test_rank_that_never_joins_ends_the_collective_with_an_error():
     for p in procs:
         p.join(timeout=30)
     assert msgs[0] == "absent" and msgs[1].startswith("error:"), msgs
+
+
+def test_peer_reducer_buffer_sets_alternate_and_never_overlap():
+    """Host arithmetic of PeerDxReducer: consecutive steps use different buffer sets,
+    a set's receive slices, row blocks and flag words stay inside the set, and the two
+    kinds of flag words of the two sets are four disjoint groups of `world` words."""
+    from fusedswiglu_b200.parallel import PeerDxReducer
+
+    T, dm, esize = 4096, 512, 2
+    for world in (2, 4, 8):
+        rows = T // world
+        words = set()
+        for seq in (1, 2, 3, 4):
+            lays = [PeerDxReducer.layout(seq, world, r, T, dm, esize) for r in range(world)]
+            s = lays[0]["set"]
+            assert s == seq & 1 and all(l["set"] == s for l in lays)
+            assert lays[0]["recv_byte_offset"] == s * T * dm * esize
+            # slice [source][rows][dm] of one set is exactly T*dm elements: sets do not overlap
+            assert world * rows * dm * esize == T * dm * esize
+            blocks = [l["my_block_elem_offset"] for l in lays]
+            assert blocks == [s * T * dm + r * rows * dm for r in range(world)]
+            assert blocks[-1] + rows * dm == (s + 1) * T * dm
+            for kind in (0, 1):
+                first = lays[0]["flag_word"][kind]
+                assert 0 <= first and first + world <= 4 * world
+                if seq <= 2:
+                    group = set(range(first, first + world))
+                    assert not (group & words)
+                    words |= group
+        assert len(words) == 4 * world
+        assert PeerDxReducer.layout(1, world, 0, T, dm, esize)["set"] != PeerDxReducer.layout(2, world, 0, T, dm, esize)["set"]
+        assert PeerDxReducer.layout(1, world, 0, T, dm, esize) == PeerDxReducer.layout(3, world, 0, T, dm, esize)
