@@ -945,6 +945,12 @@ int fsw_backward_dx_scatter(const void* dg, const void* du, const void* w_gate, 
   p.scatter_world = world;
   p.scatter_rank = rank;
   p.scatter_rows = (int)(T / world);
+  // start at the rows of the next rank; this rank's own rows (local stores) come last
+  {
+    const int tile_m = 128 * tc.cg;
+    const int m_tiles = (int)((T + tile_m - 1) / tile_m);
+    p.m_rotate = (int)((((int64_t)(rank + 1) % world) * (T / world)) / tile_m) % m_tiles;
+  }
   return run_gemm<MODE_DX>(p, (int)T, dtype, accum == FSW_ACC_F16,
                            static_cast<cudaStream_t>(stream), d, tc);
 }

@@ -104,6 +104,10 @@ struct GemmParams {
   // is laid out [source rank][scatter_rows][N].  c0_ptr is not written.
   void* scatter[8];
   int scatter_world, scatter_rank, scatter_rows;
+  // Tile rows are visited starting at row tile m_rotate (mod num_m_tiles): with the
+  // scatter every rank starts at another owner's rows, so that at any moment the
+  // ranks store to different GPUs instead of all to the same one.
+  int m_rotate;
 };
 constexpr int kMaxScatterRanks = 8;
 
@@ -138,6 +142,11 @@ constexpr int kSmemBudget = 232448;  // 227 KB opt-in limit per CTA
 // clk_probe[2..7].
 #ifndef FSW_PROFILE
 #define FSW_PROFILE 0
+#endif
+// Measurement builds only: the plain epilogue releases tensor memory after its last
+// read instead of reading everything into registers first (see drain_plain).
+#ifndef FSW_PLAIN_ONE_PHASE
+#define FSW_PLAIN_ONE_PHASE 0
 #endif
 
 template <int MODE, int CG, int NSUB>
@@ -309,6 +318,8 @@ __host__ __device__ __forceinline__ bool next_work(const GemmParams& p, int iter
   const int t = cluster_id + idx * num_clusters;
   if (t < whole) {
     decode_tile_order(t, p.num_m_tiles, p.num_n_tiles, p.group_m, w.m_tile, w.n_tile);
+    w.m_tile += p.m_rotate;
+    if (w.m_tile >= p.num_m_tiles) w.m_tile -= p.num_m_tiles;
     w.it0 = 0;
     w.it1 = iters_per_tile;
     w.slot = -1;
@@ -530,32 +541,48 @@ __device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& 
 
 // Plain epilogue over 64-column boxes jb in [jb_begin, jb_begin + NJB) of one
 // 256-column region.  MODE_DW: boxes 0,1 -> c0, boxes 2,3 -> c1, at n0 + 64*(jb&1);
-// every other mode: all four boxes belong to c0 at columns n0 + 64*jb.  Each box is read,
-// rounded, transposed through the staging buffer and written with row-coalesced
-// stores; `release` is called right after the last tensor-memory read.  (These
-// GEMMs have K loops of 400+ blocks per tile, so the few thousand cycles this
-// takes are ~1 % of a tile and are not worth the registers a two-phase drain needs.)
+// every other mode: all four boxes belong to c0 at columns n0 + 64*jb.  Two phases,
+// like the SwiGLU epilogue: first every box is read from tensor memory, rounded and
+// kept packed in registers (32 words per box) and `release` is called, so the MMA
+// issuer can start the next tile; then the boxes are transposed through the staging
+// buffer and written with row-coalesced stores beside the next tile's MMAs.  That
+// matters when a tile's K loop is short (column shards) and when the stores are slow
+// (the multi-GPU scatter writes them to peer memory over NVLink).
 template <class C, int MODE, typename T, bool ACC16, int NJB, class Release>
 __device__ __forceinline__ void drain_plain(const GemmParams& p, const EpiCtx& e, uint32_t taddr,
                                             int n0, int jb_begin, Release release) {
-#pragma unroll 1
+  uint32_t pk[NJB * 32];
+  auto read_box = [&](int j) {
+#pragma unroll
+    for (int c = 0; c < 4; c += 2)
+      load_pack16x2<T, ACC16>(taddr + (jb_begin + j) * 64 + c * 16, taddr + (jb_begin + j) * 64 + (c + 1) * 16,
+                              &pk[j * 32 + c * 8], &pk[j * 32 + (c + 1) * 8]);
+  };
+  if (!FSW_PLAIN_ONE_PHASE) {
+#pragma unroll
+    for (int j = 0; j < NJB; ++j) read_box(j);
+    release();
+  }
+  void* scatter_out = nullptr;
+  if (MODE == MODE_DX && p.scatter_world > 1) {
+    // The warp's 32 rows have one owner (scatter_rows is a multiple of 32).  Row t of
+    // dX is row (rank * scatter_rows + t - owner * scatter_rows) of the owner's buffer.
+    int owner = e.row0 / p.scatter_rows;
+    if (owner >= p.scatter_world) owner = p.scatter_world - 1;  // rows >= M: nothing is stored
+    const long long shift = static_cast<long long>(p.scatter_rank - owner) * p.scatter_rows;
+    scatter_out = static_cast<char*>(p.scatter[owner]) + shift * p.ldc * 2;
+  }
+#pragma unroll
   for (int j = 0; j < NJB; ++j) {
     const int jb = jb_begin + j;
-    uint32_t pk[32];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) load_pack16<T, ACC16>(taddr + jb * 64 + c * 16, &pk[c * 8]);
-    if (j == NJB - 1) release();
     const int col = (MODE == MODE_DW) ? (n0 + (jb & 1) * 64) : (n0 + jb * 64);
     void* out = (MODE == MODE_DW && jb >= 2) ? p.c1_ptr : p.c0_ptr;
-    if (MODE == MODE_DX && p.scatter_world > 1) {
-      // The warp's 32 rows have one owner (scatter_rows is a multiple of 32).  Row t of
-      // dX is row (rank * scatter_rows + t - owner * scatter_rows) of the owner's buffer.
-      int owner = e.row0 / p.scatter_rows;
-      if (owner >= p.scatter_world) owner = p.scatter_world - 1;  // rows >= M: nothing is stored
-      const long long shift = static_cast<long long>(p.scatter_rank - owner) * p.scatter_rows;
-      out = static_cast<char*>(p.scatter[owner]) + shift * p.ldc * 2;
+    if (MODE == MODE_DX && p.scatter_world > 1) out = scatter_out;
+    if (FSW_PLAIN_ONE_PHASE) {  // measurement build: read, release after the last read, store box by box
+      read_box(j);
+      if (j == NJB - 1) release();
     }
-    stage_rows128(e.buf, e.lane, pk);
+    stage_rows128(e.buf, e.lane, *reinterpret_cast<const uint32_t(*)[32]>(&pk[j * 32]));
     __syncwarp();
     flush_rows128(e.buf, e.lane, out, e.row0, col, p.M, p.N, p.ldc);
     __syncwarp();

@@ -307,12 +307,13 @@ class PeerDxReducer:
         with torch.cuda.stream(self.side):
             self.side.wait_event(done)
             off = lay["my_block_elem_offset"]
-            for r in range(world):
-                if r != rank:
-                    self.h_full.get_buffer(r, (rows, dm), self.dtype, off).copy_(mine, non_blocking=True)
+            # rank i sends to i+1, i+2, ...: at every moment the ranks write to different GPUs
+            order = [(rank + k) % world for k in range(1, world)]
+            for r in order:
+                self.h_full.get_buffer(r, (rows, dm), self.dtype, off).copy_(mine, non_blocking=True)
             w0, w1 = lay["flag_word"][0] + rank, lay["flag_word"][1] + rank
             src = self.flags[w0:w0 + 1]  # my own "partials arrived" word: holds seq now
-            for r in range(world):
+            for r in order + [rank]:
                 self.h_flags.get_buffer(r, (1,), torch.int32, w1).copy_(src, non_blocking=True)
 
         def finish():
