@@ -75,9 +75,10 @@ def parse_args():
     ap.add_argument("--comm-ctas", type=int, default=16, metavar="N",
                     help="N>1: CTAs NCCL may use for the dX collective (= SMs the dW GEMM leaves free beside it); "
                          "0 = NCCL's own choice on the default group with the default reservation")
-    ap.add_argument("--dx-collective", default="peer", choices=["peer", "nccl"],
-                    help="N>1: reduce dX with this library's kernels over NVLink peer memory (PeerDxReducer) "
-                         "or with NCCL beside the dW GEMM")
+    ap.add_argument("--dx-collective", default="peer", choices=["peer", "peer-copy", "nccl"],
+                    help="N>1: reduce dX with this library's kernels over NVLink peer memory (PeerDxReducer; "
+                         "peer = partial sums stored to their owners from the GEMM epilogue, peer-copy = by copy "
+                         "engines) or with NCCL beside the dW GEMM")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
@@ -420,7 +421,7 @@ def run_ours(args):
     # The dX collective runs on a group whose NCCL kernels are capped to as many CTAs
     # as the dW GEMM leaves SMs free for them.
     group = parallel.new_collective_group(max_ctas=args.comm_ctas) if world > 1 and args.comm_ctas > 0 else None
-    use_peer = world > 1 and args.dx_collective == "peer"
+    use_peer = world > 1 and args.dx_collective in ("peer", "peer-copy")
 
     _lib.load()
     for item in args.opt:
@@ -458,7 +459,6 @@ def run_ours(args):
     dout2d = dout.view(T, di_local)
 
     names = ["fwd_dual_gemm", "gate_grad_elementwise", "dx_gemm", "dw_dual_gemm"]
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(6)] for _ in range(K)]
     launches = {"n": 0}
     dw_split = {"first": None, "collective_ms": None}
 
@@ -468,44 +468,48 @@ def run_ours(args):
             return fn(*a, **kw)
         return wrapper
 
-    # Every C-ABI launch goes through these four functions; count them.
-    for _name in ("forward", "gate_grad", "grad_input", "grad_weights"):
+    # Every C-ABI kernel launch goes through these functions; count them.
+    for _name in ("forward", "gate_grad", "grad_input", "grad_weights", "grad_input_scatter", "reduce_dx_slices",
+                  "wait_flags"):
         setattr(_launch, _name, counted(getattr(_launch, _name)))
 
     class Marked:
-        """The product backend with a CUDA event recorded before each launch."""
-        marks = None
+        """The product backend with a labelled CUDA event recorded before each launch;
+        the time from one event to the next is charged to the first one's label."""
+        marks = None  # list of (label, event) of the step being timed, or None
 
         @staticmethod
-        def _mark(i):
+        def mark(label):
             if Marked.marks is not None:
-                Marked.marks[i].record()
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                Marked.marks.append((label, e))
 
         @staticmethod
         def forward(*a, **kw):
-            Marked._mark(0)
+            Marked.mark("fwd_dual_gemm")
             return _launch.forward(*a, **kw)
 
         @staticmethod
         def gate_grad(*a, **kw):
-            Marked._mark(1)
+            Marked.mark("gate_grad_elementwise")
             return _launch.gate_grad(*a, **kw)
 
         @staticmethod
         def grad_input(*a, **kw):
-            Marked._mark(2)
+            Marked.mark("dx_gemm")
             return _launch.grad_input(*a, **kw)
 
         @staticmethod
         def grad_weights(*a, **kw):
-            Marked._mark(3)
+            Marked.mark("dw_dual_gemm")
             r = _launch.grad_weights(*a, **kw)
-            Marked._mark(4)
+            Marked.mark("after_dw")
             return r
 
         @staticmethod
         def grad_weights_beside_collective(x2d_, dg, du, **kw):
-            Marked._mark(3)
+            Marked.mark("dw_dual_gemm")
             if dw_split["first"] is None and kw.get("work") is not None:
                 dw_split["collective_ms"] = (kw.get("collective_s") or 0.0) * 1e3
                 dw_split["first"] = parallel.plan_dw_split(
@@ -513,7 +517,7 @@ def run_ours(args):
                     _lib.get_option("sm_count"), parallel.comm_sms(world, kw.get("group")), x2d_.element_size(),
                     kw.get("collective", "all_reduce"), kw.get("collective_s"))
             r = parallel._CudaBackend.grad_weights_beside_collective(x2d_, dg, du, **kw)
-            Marked._mark(4)
+            Marked.mark("after_dw")
             return r
 
     wgp = wg.clone().requires_grad_(True)
@@ -521,37 +525,47 @@ def run_ours(args):
 
     reducer = None
     if use_peer:
-        real_reducer = parallel.PeerDxReducer(T, dm, tdt, dev, group)
+        real_reducer = parallel.PeerDxReducer(T, dm, tdt, dev, group,
+                                              scatter="copy" if args.dx_collective == "peer-copy" else "epilogue")
 
         class MarkedReducer:
+            """The product's reducer with the same labelled events."""
+            columns_before_reduction = staticmethod(real_reducer.columns_before_reduction)
+
+            @staticmethod
+            def scatter(*a, **kw):
+                Marked.mark("dx_gemm")
+                return real_reducer.scatter(*a, **kw)
+
             @staticmethod
             def reduce(*a, **kw):
-                Marked._mark(2)
-                launches["n"] += 2  # the scattering dX GEMM and the reduction kernel
-                return real_reducer.reduce(*a, **kw)
+                Marked.mark("dx_reduction")
+                r = real_reducer.reduce(*a, **kw)
+                Marked.mark("after_dw")
+                return r
 
         reducer = MarkedReducer
+        dw_split["first"] = real_reducer.columns_before_reduction(di_local, False)
 
     def step(marks=None):
         """One forward + backward.  world == 1: the launch sequence of FusedSwiGLU
         (the autograd Function adds nothing on the device).  world > 1: the package's
         ColumnParallelSwiGLU forward and backward themselves."""
+        Marked.marks = marks
         if world == 1:
-            Marked.marks = marks
             out, gg, uu = Marked.forward(x2d, wg, wu, fast_accum=fast)
             dg, du = Marked.gate_grad(dout2d, gg, uu)
             dx = Marked.grad_input(dg, du, wg, wu)
             dwg, dwu = Marked.grad_weights(x2d, dg, du, fast_accum=fast)
-            if marks: marks[5].record()
+            Marked.mark("end")
             Marked.marks = None
             return out, dx, dwg, dwu
         xin = x.detach().requires_grad_(True)
         wgp.grad = wup.grad = None
-        Marked.marks = marks
         out = parallel.column_parallel_swiglu(xin, wgp, wup, group=group, fast_accum=fast, backend=Marked,
                                               reducer=reducer)
         out.backward(dout)
-        if marks: marks[5].record()
+        Marked.mark("end")
         Marked.marks = None
         return out.detach().view(T, di_local), xin.grad.view(T, dm), wgp.grad, wup.grad
 
@@ -616,8 +630,9 @@ def run_ours(args):
     launches["n"] = 0
     wall0 = time.time()
     t_start.record()
+    step_marks = [[] for _ in range(K)]
     for i in range(K):
-        step(ev[i])
+        step(step_marks[i])
     t_end.record()
     barrier()
     wall1 = time.time()
@@ -628,8 +643,15 @@ def run_ours(args):
         pre = ClockSampler.summary(sampler, pre0, wall0, "pre-heat and warm-up (same step loop)")
         clocks["before_timed_region"] = {k: pre[k] for k in ("sm_mhz", "reasons", "samples", "window")}
     total_ms = t_start.elapsed_time(t_end)
-    per_kernel_ms = [sum(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(K)) / K for j in range(4)]
-    tail_ms = sum(ev[i][4].elapsed_time(ev[i][5]) for i in range(K)) / K  # collective left exposed after dW
+    by_label = {}
+    for marks in step_marks:
+        for (label, e0), (_, e1) in zip(marks, marks[1:]):
+            by_label[label] = by_label.get(label, 0.0) + e0.elapsed_time(e1) / K
+    per_kernel_ms = [by_label.get(n, 0.0) for n in names]
+    # "after_dw": between the end of a dW launch and whatever follows it - at the end of
+    # the step that is the part of the collective left exposed
+    tail_ms = by_label.get("after_dw", 0.0)
+    reduction_ms = by_label.get("dx_reduction")
     if world > 1:
         tt = torch.tensor([total_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -830,10 +852,12 @@ def run_ours(args):
             kern[n] = {"ms": ms, "achieved": tf, "unit": "TFLOP/s", "bound": "tensor",
                        "frac": tf / peaks["bf16_tflops_sustained"]}
     if world > 1 and use_peer:
-        kern["dx_gemm"]["note"] = ("includes the reduction: the GEMM's epilogue stores the partial sums into the "
-                                   "owning ranks' buffers over NVLink, a second kernel waits for the peers and adds "
-                                   "the slices")
-        kern["dw_dual_gemm"]["note"] = "runs on all SMs while copy engines gather the reduced row blocks"
+        kern["dx_gemm"]["note"] = ("the GEMM's epilogue stores the partial sums into the owning ranks' buffers "
+                                   "over NVLink")
+        kern["dx_reduction"] = {"ms": reduction_ms, "note": "waits (time-limited) for the peers' partials, adds the "
+                                                            "slices in fp32; queued between two column ranges of dW"}
+        kern["dw_dual_gemm"]["note"] = ("all SMs, in two column ranges around the reduction; copy engines gather "
+                                        "the reduced row blocks beside the second")
         kern["collective_exposed_after_dw"] = {"ms": tail_ms}
     elif world > 1:
         kern["dw_dual_gemm"]["note"] = ("runs beside the NCCL all-reduce of dX; first column range on "

@@ -200,13 +200,13 @@ def grad_input_scatter(dg: torch.Tensor, du: torch.Tensor, w_gate: torch.Tensor,
 
 
 def reduce_dx_slices(recv_ptr: int, peer_flag_ptrs, my_flags_ptr: int, world: int, rank: int, seq: int,
-                     out: torch.Tensor) -> None:
+                     out: torch.Tensor, own_slice: Optional[torch.Tensor] = None) -> None:
     """Signal the peers, wait (bounded) for their partials and sum the ``world`` slices
     of this rank's receive buffer into ``out`` (rows, dm); see fsw_dx_reduce."""
     rows, dm = out.shape
     with torch.cuda.device(out.device):
         rc = _lib.load().fsw_dx_reduce(
-            recv_ptr, _ptr_array(peer_flag_ptrs), my_flags_ptr, int(world), int(rank), int(seq) & 0xFFFFFFFF,
+            recv_ptr, own_slice.data_ptr() if own_slice is not None else None, _ptr_array(peer_flag_ptrs), my_flags_ptr, int(world), int(rank), int(seq) & 0xFFFFFFFF,
             rows, dm, out.data_ptr(), _code(out), _stream(out),
         )
     _lib.check("fsw_dx_reduce", rc)

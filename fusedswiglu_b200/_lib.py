@@ -21,7 +21,7 @@ SIGNATURES = {
     "fsw_backward_elementwise": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_void_p]),
     "fsw_backward_dx": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_backward_dx_scatter": (c_int, [c_void_p] * 4 + [POINTER(c_void_p), c_int, c_int] + [c_int64] * 3 + [c_int, c_int, c_void_p]),
-    "fsw_dx_reduce": (c_int, [c_void_p, POINTER(c_void_p), c_void_p, c_int, c_int, c_uint32, c_int64, c_int64, c_void_p, c_int, c_void_p]),
+    "fsw_dx_reduce": (c_int, [c_void_p, c_void_p, POINTER(c_void_p), c_void_p, c_int, c_int, c_uint32, c_int64, c_int64, c_void_p, c_int, c_void_p]),
     "fsw_wait_flags": (c_int, [c_void_p, c_int, c_uint32, c_void_p]),
     "fsw_backward_dw": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_backward_dw_columns": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_int, c_void_p, c_int64, c_int, c_int, c_void_p]),

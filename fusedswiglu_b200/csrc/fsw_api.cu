@@ -57,6 +57,7 @@ struct Options {
   int64_t pace_limit_us = 50;    // longest wait at one meeting point
   int64_t ew_blocks_per_sm = 32;  // grid cap of the elementwise kernel, per SM
   int64_t split_k = 1;            // 0: never split the last wave of tiles along K
+  int64_t scatter_gap_ns = -1;    // pause between peer-store instructions of the dX scatter; -1 = from the tile's length
 };
 static Options g_opt;
 
@@ -742,6 +743,9 @@ int fsw_set_option(const char* name, int64_t value) {
   } else if (!strcmp(name, "split_k")) {
     if (value != 0 && value != 1) return fail(FSW_EINVAL, "split_k must be 0 or 1");
     g_opt.split_k = value;
+  } else if (!strcmp(name, "scatter_gap_ns")) {
+    if (value < -1 || value > 100000) return fail(FSW_EINVAL, "scatter_gap_ns must be in [-1, 100000]");
+    g_opt.scatter_gap_ns = value;
   } else if (!strcmp(name, "ew_blocks_per_sm")) {
     if (value < 1 || value > 64) return fail(FSW_EINVAL, "ew_blocks_per_sm must be in [1, 64]");
     g_opt.ew_blocks_per_sm = value;
@@ -758,6 +762,7 @@ int64_t fsw_get_option(const char* name) {
   if (!strcmp(name, "nsub")) return g_opt.nsub;
   if (!strcmp(name, "ew_blocks_per_sm")) return g_opt.ew_blocks_per_sm;
   if (!strcmp(name, "split_k")) return g_opt.split_k;
+  if (!strcmp(name, "scatter_gap_ns")) return g_opt.scatter_gap_ns;
   if (!strcmp(name, "gemm_max_sms")) return g_opt.gemm_max_sms;
   if (!strcmp(name, "wait_limit_ms")) return g_opt.wait_limit_ms;
   if (!strcmp(name, "stall_producer")) return g_opt.stall_producer;
@@ -945,6 +950,15 @@ int fsw_backward_dx_scatter(const void* dg, const void* du, const void* w_gate, 
   p.scatter_world = world;
   p.scatter_rank = rank;
   p.scatter_rows = (int)(T / world);
+  // Spread a tile's 32 store instructions per warp over about 60 % of the tile's K loop
+  // (0.8 us per K block of a 256x512 tile at the sustained rate).
+  if (g_opt.scatter_gap_ns >= 0) {
+    p.scatter_gap_ns = (unsigned int)g_opt.scatter_gap_ns;
+  } else {
+    const double tile_ns = 2.0 * p.num_k_blocks * 800.0;
+    double gap = 0.6 * tile_ns / 32.0;
+    p.scatter_gap_ns = (unsigned int)(gap > 4000.0 ? 4000.0 : gap);
+  }
   // start at the rows of the next rank; this rank's own rows (local stores) come last
   {
     const int tile_m = 128 * tc.cg;
@@ -955,14 +969,16 @@ int fsw_backward_dx_scatter(const void* dg, const void* du, const void* w_gate, 
                            static_cast<cudaStream_t>(stream), d, tc);
 }
 
-int fsw_dx_reduce(const void* recv, void* const* peer_flag_ptrs, void* my_flags, int world, int rank,
-                  uint32_t seq, int64_t rows, int64_t dm, void* dx_rows, int dtype, void* stream) {
+int fsw_dx_reduce(const void* recv, const void* own_slice, void* const* peer_flag_ptrs, void* my_flags,
+                  int world, int rank, uint32_t seq, int64_t rows, int64_t dm, void* dx_rows, int dtype,
+                  void* stream) {
   if (dtype != FSW_BF16 && dtype != FSW_FP16) return fail(FSW_EINVAL, "unknown dtype %d", dtype);
   if (world < 2 || world > kMaxScatterRanks || rank < 0 || rank >= world)
     return fail(FSW_EINVAL, "world size %d (2..%d) / rank %d", world, kMaxScatterRanks, rank);
   if (rows <= 0 || dm <= 0 || (dm & 7)) return fail(FSW_EINVAL, "bad shape rows=%lld dm=%lld", (long long)rows, (long long)dm);
   if (!recv || !peer_flag_ptrs || !my_flags || !dx_rows) return fail(FSW_EINVAL, "NULL pointer");
-  if (!aligned16(recv) || !aligned16(dx_rows) || (reinterpret_cast<uintptr_t>(my_flags) & 3u))
+  if (!aligned16(recv) || !aligned16(own_slice) || !aligned16(dx_rows) ||
+      (reinterpret_cast<uintptr_t>(my_flags) & 3u))
     return fail(FSW_EINVAL, "pointers must be aligned (16 bytes; flags 4 bytes)");
   PeerFlags pf;
   memset(&pf, 0, sizeof(pf));
@@ -982,11 +998,12 @@ int fsw_dx_reduce(const void* recv, void* const* peer_flag_ptrs, void* my_flags,
   const unsigned long long limit = (unsigned long long)g_opt.wait_limit_ms * 1000000ull;
   if (dtype == FSW_BF16)
     dx_slices_reduce_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
-        static_cast<const uint4*>(recv), static_cast<__nv_bfloat16*>(dx_rows), vecs, world, rank, seq,
-        pf, static_cast<unsigned int*>(my_flags), d->status, limit);
+        static_cast<const uint4*>(recv), static_cast<const uint4*>(own_slice),
+        static_cast<__nv_bfloat16*>(dx_rows), vecs, world, rank, seq, pf, static_cast<unsigned int*>(my_flags), d->status, limit);
   else
     dx_slices_reduce_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(
-        static_cast<const uint4*>(recv), static_cast<__half*>(dx_rows), vecs, world, rank, seq, pf,
+        static_cast<const uint4*>(recv), static_cast<const uint4*>(own_slice),
+        static_cast<__half*>(dx_rows), vecs, world, rank, seq, pf,
         static_cast<unsigned int*>(my_flags), d->status, limit);
   FSW_CUDA(cudaGetLastError());
   return FSW_OK;

@@ -104,6 +104,13 @@ struct GemmParams {
   // is laid out [source rank][scatter_rows][N].  c0_ptr is not written.
   void* scatter[8];
   int scatter_world, scatter_rank, scatter_rows;
+  // Pause between two store instructions of a warp that go to peer memory.  Without it
+  // all CTAs emit a tile's rows in one burst at the end of each wave of tiles; NVLink
+  // (~690 GB/s for SM-issued stores, measured) drains that for tens of microseconds,
+  // the stores back up into the SMs' request path and the TMA loads of the next tile
+  // queue behind them.  Spread over most of a tile's K loop the same bytes never
+  // exceed the link's rate.
+  unsigned int scatter_gap_ns;
   // Tile rows are visited starting at row tile m_rotate (mod num_m_tiles): with the
   // scatter every rank starts at another owner's rows, so that at any moment the
   // ranks store to different GPUs instead of all to the same one.
@@ -396,10 +403,11 @@ __device__ __forceinline__ void stage_rows128(uint32_t buf, int lane, const uint
     ptx::st_shared_v4(base + ((c ^ x) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
 }
 __device__ __forceinline__ void flush_rows128(uint32_t buf, int lane, void* out, int row0, int col0,
-                                              int M, int N, int ld) {
+                                              int M, int N, int ld, unsigned int gap_ns = 0) {
   const int c = lane & 7;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
+    if (gap_ns != 0) __nanosleep(gap_ns);
     const int r = 4 * i + (lane >> 3);
     uint32_t a, b, cc, d;
     ptx::ld_shared_v4(buf + r * 128u + ((c ^ (r & 7)) << 4), a, b, cc, d);
@@ -564,6 +572,7 @@ __device__ __forceinline__ void drain_plain(const GemmParams& p, const EpiCtx& e
     release();
   }
   void* scatter_out = nullptr;
+  unsigned int gap_ns = 0;
   if (MODE == MODE_DX && p.scatter_world > 1) {
     // The warp's 32 rows have one owner (scatter_rows is a multiple of 32).  Row t of
     // dX is row (rank * scatter_rows + t - owner * scatter_rows) of the owner's buffer.
@@ -571,6 +580,7 @@ __device__ __forceinline__ void drain_plain(const GemmParams& p, const EpiCtx& e
     if (owner >= p.scatter_world) owner = p.scatter_world - 1;  // rows >= M: nothing is stored
     const long long shift = static_cast<long long>(p.scatter_rank - owner) * p.scatter_rows;
     scatter_out = static_cast<char*>(p.scatter[owner]) + shift * p.ldc * 2;
+    if (owner != p.scatter_rank) gap_ns = p.scatter_gap_ns;
   }
 #pragma unroll
   for (int j = 0; j < NJB; ++j) {
@@ -584,7 +594,7 @@ __device__ __forceinline__ void drain_plain(const GemmParams& p, const EpiCtx& e
     }
     stage_rows128(e.buf, e.lane, *reinterpret_cast<const uint32_t(*)[32]>(&pk[j * 32]));
     __syncwarp();
-    flush_rows128(e.buf, e.lane, out, e.row0, col, p.M, p.N, p.ldc);
+    flush_rows128(e.buf, e.lane, out, e.row0, col, p.M, p.N, p.ldc, gap_ns);
     __syncwarp();
   }
 }
@@ -1113,8 +1123,8 @@ struct PeerFlags {
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-    dx_slices_reduce_kernel(const uint4* __restrict__ recv, T* __restrict__ out, long long vecs_per_slice,
-                            int world, int rank, unsigned int seq, const PeerFlags peer_flags,
+    dx_slices_reduce_kernel(const uint4* __restrict__ recv, const uint4* __restrict__ own_slice,
+                            T* __restrict__ out, long long vecs_per_slice, int world, int rank, unsigned int seq, const PeerFlags peer_flags,
                             volatile unsigned int* my_flags, uint32_t* status,
                             unsigned long long wait_limit_ns) {
   __shared__ int give_up;
@@ -1147,21 +1157,40 @@ __global__ void __launch_bounds__(256)
   }
   __syncthreads();
   if (give_up) return;
+  // every slice vector of a thread is loaded before the first is used
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < vecs_per_slice;
        v += stride) {
+    uint4 w[kMaxScatterRanks];
+#pragma unroll
+    for (int s = 0; s < kMaxScatterRanks; ++s) {
+      if (s < world) {
+        // this rank's own partial may sit outside the receive buffer (it never left the GPU)
+        const uint4* src = (s == rank && own_slice != nullptr)
+                               ? own_slice + v
+                               : recv + static_cast<long long>(s) * vecs_per_slice + v;
+        // a coherent load (not the read-only path): peers wrote these lines until just
+        // before the flags were seen
+        asm volatile("ld.global.L1::no_allocate.v4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(w[s].x), "=r"(w[s].y), "=r"(w[s].z), "=r"(w[s].w)
+                     : "l"(src)
+                     : "memory");
+      }
+    }
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int s = 0; s < world; ++s) {
-      const uint4 w = recv[static_cast<long long>(s) * vecs_per_slice + v];
-      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float lo, hi;
-        unpack2<T>(ww[e], lo, hi);
-        acc[2 * e] += lo;
-        acc[2 * e + 1] += hi;
+    for (int s = 0; s < kMaxScatterRanks; ++s) {
+      if (s < world) {
+        const uint32_t ww[4] = {w[s].x, w[s].y, w[s].z, w[s].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float lo, hi;
+          unpack2<T>(ww[e], lo, hi);
+          acc[2 * e] += lo;
+          acc[2 * e + 1] += hi;
+        }
       }
     }
     uint4 o;

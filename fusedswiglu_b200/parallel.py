@@ -111,6 +111,7 @@ ALLREDUCE_BUS_BYTES_PER_S_OTHER = 225e9
 ALLREDUCE_FIXED_S = 40e-6
 GEMM_SUSTAINED_FLOPS = 1.35e15
 DW_SPLIT_ALIGN = 256  # columns per dW tile
+GATHER_BYTES_PER_S = 650e9  # copy-engine peer copies into one GPU over NVLink (measured: ~700 GB/s per pair)
 
 
 def plan_dw_split(T: int, dm: int, di_local: int, world_size: int, sm_count: int, reserve: int,
@@ -226,11 +227,21 @@ class PeerDxReducer:
     one step ahead of a peer, never two, because its reduction waits for every peer's
     signal of the same step.
 
+    ``scatter="copy"`` is the variant without peer stores from the GEMM: the dX GEMM
+    writes its partial sums locally at full speed and copy engines carry each row block
+    to its owner (beside the first column range of the dW GEMM); reduction and gather are
+    the same.  It moves the same bytes without any SM stalling on NVLink stores, but needs
+    a dW GEMM long enough to cover two rounds of copies.
+
     In replicated-x mode the returned dX is a view of an internal buffer that the
     second-next call overwrites; pass ``own_output=True`` to get a private copy.
     Collective: construct it on all ranks of ``group`` at the same point."""
 
-    def __init__(self, T: int, dm: int, dtype: torch.dtype, device, group=None, own_output: bool = False):
+    def __init__(self, T: int, dm: int, dtype: torch.dtype, device, group=None, own_output: bool = False,
+                 scatter: str = "epilogue"):
+        if scatter not in ("epilogue", "copy"):
+            raise ValueError("scatter must be 'epilogue' or 'copy'")
+        self.scatter_mode = scatter
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer access only
         import torch.distributed._symmetric_memory as symm_mem
 
@@ -280,22 +291,67 @@ class PeerDxReducer:
     def _flag_ptrs(self, s, kind):
         return [p + ((s * 2 + kind) * self.world) * 4 for p in self.h_flags.buffer_ptrs]
 
-    def reduce(self, dg, du, w_gate, w_up, row_sharded: bool):
-        """Queue the scattering dX GEMM and the reduction on the current stream.
-        Returns (dx, finish): call ``finish()`` after queueing the work that should
-        overlap the gather (the dW GEMM); dx is valid on the current stream after it."""
+    def scatter(self, dg, du, w_gate, w_up) -> None:
+        """Queue this step's dX GEMM; its epilogue stores the partial sums into the
+        owning ranks' receive buffers."""
         self.seq += 1
-        seq, rank, world, rows, dm = self.seq, self.rank, self.world, self.rows, self.dm
-        lay = self.layout(seq, world, rank, self.T, dm, self.esize)
-        s = lay["set"]
-        _launch.grad_input_scatter(dg, du, w_gate, w_up, self._recv_ptrs(s), world, rank)
+        self._lay = lay = self.layout(self.seq, self.world, self.rank, self.T, self.dm, self.esize)
+        self._copied = None
+        if self.scatter_mode == "epilogue":
+            _launch.grad_input_scatter(dg, du, w_gate, w_up, self._recv_ptrs(lay["set"]), self.world, self.rank)
+            return
+        # copy engines carry the row blocks of the locally written partial dX to their owners
+        rank, world, rows, dm = self.rank, self.world, self.rows, self.dm
+        self._partial = partial = _launch.grad_input(dg, du, w_gate, w_up)
+        done = torch.cuda.Event()
+        done.record()
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(done)
+            off = lay["set"] * self.T * dm + rank * rows * dm  # slice [this rank] of the owner's buffer
+            for r in [(rank + k) % world for k in range(1, world)]:  # the own block stays where it is
+                self.h_recv.get_buffer(r, (rows, dm), self.dtype, off).copy_(partial[r * rows:(r + 1) * rows],
+                                                                             non_blocking=True)
+            self._copied = torch.cuda.Event()
+            self._copied.record()
+
+    def columns_before_reduction(self, di_local: int, row_sharded: bool) -> int:
+        """How many columns of the local dW GEMM to queue between scatter() and reduce().
+
+        The reduction waits for the slowest peer's dX GEMM; GEMM work queued before it
+        absorbs that wait.  In replicated-x mode the rest of dW, queued after it, must
+        still last as long as the gather of the row blocks (copy engines, about
+        650 GB/s into each GPU), or the gather is left exposed."""
         if row_sharded:
-            mine = torch.empty((rows, dm), device=dg.device, dtype=dg.dtype)
+            return di_local
+        nbytes = (self.world - 1) * self.rows * self.dm * self.esize
+        t_gather = 1.15 * (nbytes / GATHER_BYTES_PER_S + 30e-6)
+        t_dw = 4.0 * self.T * self.dm * di_local / GEMM_SUSTAINED_FLOPS
+        if self.scatter_mode == "copy" and 2 * t_gather >= t_dw:
+            # two rounds of copies (to the owners, then the gather) and a GEMM too short to
+            # cover both: give each round half of it
+            return (di_local // 2) // DW_SPLIT_ALIGN * DW_SPLIT_ALIGN
+        after = min(1.0, t_gather / t_dw) * di_local
+        after = min(di_local, -(-int(after) // DW_SPLIT_ALIGN) * DW_SPLIT_ALIGN)
+        return di_local - after
+
+    def reduce(self, row_sharded: bool):
+        """Queue the reduction of this step's partials (after scatter()).  Returns
+        (dx, finish): call ``finish()`` after queueing the work that should overlap
+        the gather; dx is valid on the current stream after it."""
+        seq, rank, world, rows, dm, lay = self.seq, self.rank, self.world, self.rows, self.dm, self._lay
+        s = lay["set"]
+        if self._copied is not None:
+            # the kernel below tells the peers that this rank's partials have arrived:
+            # true only once the copies have
+            torch.cuda.current_stream(self.device).wait_event(self._copied)
+        if row_sharded:
+            mine = torch.empty((rows, dm), device=self.device, dtype=self.dtype)
         else:
             full = self.full[lay["full_elem_offset"]:lay["full_elem_offset"] + self.T * dm].view(self.T, dm)
             mine = full[rank * rows:(rank + 1) * rows]
+        own = self._partial[rank * rows:(rank + 1) * rows] if self._copied is not None else None
         _launch.reduce_dx_slices(self._recv_ptrs(s)[rank], self._flag_ptrs(s, 0), self._flag_ptrs(s, 0)[rank],
-                                 world, rank, seq, mine)
+                                 world, rank, seq, mine, own_slice=own)
         if row_sharded:
             return mine, (lambda: mine)
         # gather: my reduced rows to every peer's copy of the full dX, then my step
@@ -303,7 +359,6 @@ class PeerDxReducer:
         # queued on a side stream, ordered after the reduction
         done = torch.cuda.Event()
         done.record()
-        main = torch.cuda.current_stream(dg.device)
         with torch.cuda.stream(self.side):
             self.side.wait_event(done)
             off = lay["my_block_elem_offset"]
@@ -378,8 +433,17 @@ class ColumnParallelSwiGLU(Function):
         if reducer is not None:
             # this library's own reduce-scatter over peer memory: no NCCL kernel needs
             # SMs, so the dW GEMM keeps the whole GPU while the row blocks are gathered
-            dx, finish = reducer.reduce(dg, du, wg, wu, sharded)
-            dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=fast_accum)
+            reducer.scatter(dg, du, wg, wu)
+            di_local = wg.shape[1]
+            first = reducer.columns_before_reduction(di_local, sharded)
+            dwg = dwu = None
+            if first > 0:  # GEMM work that absorbs the wait for the slowest peer's dX
+                dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=fast_accum,
+                                                **({} if first == di_local else {"columns": (0, first)}))
+            dx, finish = reducer.reduce(sharded)
+            if first < di_local:  # ... and the rest of dW beside the gather of the row blocks
+                dwg, dwu = backend.grad_weights(x2d, dg, du, fast_accum=fast_accum, out_gate=dwg, out_up=dwu,
+                                                columns=(first, di_local - first))
             dx = finish()
             return dx.view(bs, sq, dm), dwg, dwu, None, None, None, None, None
         dx = backend.grad_input(dg, du, wg, wu)

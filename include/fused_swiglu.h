@@ -146,7 +146,8 @@ int fsw_backward(const void* dout, const void* x, const void* w_gate, const void
  * each rank's `world` 32-bit flag words), waits until all `world` words of my_flags
  * have reached `seq` - i.e. every peer's partials for these rows have arrived - and
  * writes the fp32 sum of the `world` slices of `recv` (this rank's buffer), rounded
- * once, to dx_rows (T/world, dm).  `seq` must grow by one per step, and the receive
+ * once, to dx_rows (T/world, dm); if own_slice is not NULL, slice [rank] is read from
+ * there instead (a caller that moves the partials with copies need not copy its own).  `seq` must grow by one per step, and the receive
  * buffers and flag arrays must alternate between two sets from step to step (a rank
  * may be one step ahead of a peer, never two).  The wait gives up after
  * "wait_limit_ms": the kernel then records a code in the status word (fsw_status)
@@ -157,8 +158,9 @@ int fsw_backward(const void* dout, const void* x, const void* w_gate, const void
 int fsw_backward_dx_scatter(const void* dg, const void* du, const void* w_gate, const void* w_up,
                             void* const* recv_ptrs, int world, int rank, int64_t T, int64_t dm,
                             int64_t di, int dtype, int accum, void* stream);
-int fsw_dx_reduce(const void* recv, void* const* peer_flag_ptrs, void* my_flags, int world, int rank,
-                  uint32_t seq, int64_t rows, int64_t dm, void* dx_rows, int dtype, void* stream);
+int fsw_dx_reduce(const void* recv, const void* own_slice, void* const* peer_flag_ptrs, void* my_flags,
+                  int world, int rank, uint32_t seq, int64_t rows, int64_t dm, void* dx_rows, int dtype,
+                  void* stream);
 int fsw_wait_flags(void* flags, int n, uint32_t seq, void* stream);
 
 /*

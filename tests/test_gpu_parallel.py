@@ -69,9 +69,11 @@ def _worker(rank, world, port, q):
 
         # the same two modes with the dX collective done by the library's own kernels over
         # NVLink peer memory (three steps: both buffer sets and their reuse are exercised)
-        reducer = parallel.PeerDxReducer(bs * sq, dm, torch.bfloat16, torch.device("cuda", rank))
+        reducers = {mode: parallel.PeerDxReducer(bs * sq, dm, torch.bfloat16, torch.device("cuda", rank), scatter=mode)
+                    for mode in ("epilogue", "copy")}
         peer = {}
-        for step in range(3):
+        for step in range(6):
+            reducer = reducers["epilogue" if step < 3 else "copy"]
             x3 = x0.clone().requires_grad_(True)
             wg3 = parallel.shard_columns(wg0, rank, world).requires_grad_(True)
             wu3 = parallel.shard_columns(wu0, rank, world).requires_grad_(True)
@@ -151,7 +153,7 @@ def test_two_gpu_column_parallel_matches_single_gpu():
         rs = r["row_sharded"]
         assert rs["out_equal"] and rs["dwg_equal"] and rs["dwu_equal"] and rs["dx_shape_ok"], (rank, rs)
         assert rs["dx_rel"] < 1e-2, (rank, rs)
-        for step in range(3):
+        for step in range(6):  # steps 0-2: partial sums stored by the GEMM epilogue, 3-5: by copy engines
             pr = r["peer"][step]
             assert pr["dx_rel"] < 1e-2 and pr["dx_rows_rel"] < 1e-2, (rank, step, pr)
             assert pr["dx_rows_equal_full"] and pr["dw_equal"], (rank, step, pr)
