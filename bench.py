@@ -89,7 +89,7 @@ def parse_args():
                     help="fp16 workloads: accumulate in fp32 instead of the fp16 accumulator")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="library tuning knob passed to fsw_set_option, e.g. --opt group_m=16 (repeatable)")
-    ap.add_argument("--only", default=None, choices=["fwd", "ew", "dx", "dw"],
+    ap.add_argument("--only", default=None, choices=["fwd", "ew", "dx", "dw", "fwdst", "dxf"],
                     help="launch only this kernel in each step (for profiling one kernel); prints no bench line")
     ap.add_argument("--shard-of", type=int, default=1, metavar="N",
                     help="with --only on one GPU: time rank 0's 1/N column shard of the workload")
@@ -583,7 +583,13 @@ def run_ours(args):
             "ew": lambda: _launch.gate_grad(dout2d, gg, uu),
             "dx": lambda: _launch.grad_input(dg, du, wg, wu),
             "dw": lambda: _launch.grad_weights(x2d, dg, du, fast_accum=fast),
+            # the gate gradient inside the dX GEMM: forward that saves silu(g) and u*silu'(g), fused dX
+            "fwdst": lambda: _launch.forward(x2d, wg, wu, fast_accum=fast, save_factors=True),
+            "dxf": None,
         }[args.only]
+        if args.only == "dxf":
+            _, sf, tf = _launch.forward(x2d, wg, wu, fast_accum=fast, save_factors=True)
+            one = lambda: _launch.grad_input_fused(dout2d, sf, tf, wg, wu)
         for _ in range(W):
             one()
         barrier()

@@ -14,7 +14,11 @@ Differences, all on the accurate side of the reference's tolerances:
     (1, d_model, d_intermediate) to that shape anyway;
   * gradients that autograd does not need are not computed;
   * with ``recompute`` the saved x@w_gate and x@w_up are dropped and recomputed in
-    backward (an activation-memory mode the reference does not have).
+    backward (an activation-memory mode the reference does not have);
+  * with ``fused_gate_grad`` the forward saves s = silu(g) and t = u*silu'(g) instead
+    of g and u, and the gate-gradient step runs inside the dX GEMM (one launch for
+    kernels_bf16.py:210-255 + swiglu.py:45): dg = dout*t, du = dout*s, one rounding
+    apart from the reference's order (dout*u first, then *silu'(g)).
 """
 from __future__ import annotations
 
@@ -23,7 +27,8 @@ import torch
 from . import _launch
 
 
-def swiglu_forward(ctx, x, w_gate, w_up, *, fast_accum: bool, recompute: bool = False):
+def swiglu_forward(ctx, x, w_gate, w_up, *, fast_accum: bool, recompute: bool = False,
+                   fused_gate_grad: bool = False):
     assert (
         x.shape[2] == w_up.shape[0]
     ), f"Dimension mismatch. Expected a.shape[2] ({x.shape[2]}) to be equal to b.shape[0] ({w_up.shape[0]})"
@@ -41,7 +46,9 @@ def swiglu_forward(ctx, x, w_gate, w_up, *, fast_accum: bool, recompute: bool = 
     # recompute: keep only x and the weights; backward runs the forward kernel again to
     # get g and u (bit-identical), trading one extra dual GEMM for 2*T*di saved elements.
     save_gu = need_grad and not recompute
-    out, g, u = _launch.forward(x2d, wg, wu, fast_accum=fast_accum, save_activations=save_gu)
+    ctx.fused_gate_grad = bool(fused_gate_grad)
+    out, g, u = _launch.forward(x2d, wg, wu, fast_accum=fast_accum, save_activations=save_gu,
+                                save_factors=save_gu and ctx.fused_gate_grad)
     if save_gu:
         ctx.save_for_backward(x2d, wg, wu, g, u)
     elif need_grad:
@@ -55,17 +62,25 @@ def swiglu_backward(ctx, grad_output, *, fast_accum: bool):
         x2d, wg, wu, g, u = ctx.saved_tensors
     else:
         x2d, wg, wu = ctx.saved_tensors
-        _, g, u = _launch.forward(x2d, wg, wu, fast_accum=fast_accum, save_activations=True)
+        _, g, u = _launch.forward(x2d, wg, wu, fast_accum=fast_accum, save_activations=True,
+                                  save_factors=ctx.fused_gate_grad)
     bs, sq, dm = ctx.in_shape
     di = wg.shape[1]
     need_x, need_g, need_u = ctx.needs_input_grad[:3]
     dout = grad_output.contiguous().view(bs * sq, di)
     if dout.dtype != x2d.dtype:
         dout = dout.to(x2d.dtype)
-    dg, du = _launch.gate_grad(dout, g, u)
     dx = dwg = dwu = None
-    if need_x:
-        dx = _launch.grad_input(dg, du, wg, wu).view(bs, sq, dm)
+    if ctx.fused_gate_grad:  # g and u hold the saved factors s and t
+        if need_x:
+            dx, dg, du = _launch.grad_input_fused(dout, g, u, wg, wu)
+            dx = dx.view(bs, sq, dm)
+        else:
+            dg, du = _launch.gate_grad_from_factors(dout, g, u)
+    else:
+        dg, du = _launch.gate_grad(dout, g, u)
+        if need_x:
+            dx = _launch.grad_input(dg, du, wg, wu).view(bs, sq, dm)
     if need_g or need_u:
         dwg, dwu = _launch.grad_weights(x2d, dg, du, fast_accum=fast_accum)
         dwg = dwg if need_g else None

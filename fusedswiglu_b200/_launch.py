@@ -61,9 +61,24 @@ def forward(
     fast_accum: bool = False,
     save_activations: bool = True,
     split_k: bool = True,
+    save_factors: bool = False,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """out, g, u for x2d (T, dm) and weights (dm, di); g and u are None when not saved.
-    ``split_k`` lets the last partial wave of tiles be divided along K (needs scratch)."""
+    ``split_k`` lets the last partial wave of tiles be divided along K (needs scratch).
+    ``save_factors``: return (out, s, t) with s = silu(g) and t = u * silu'(g), the two
+    factors the fused backward multiplies dout by, instead of g and u."""
+    if save_factors:
+        _require_cuda(x2d, w_gate, w_up)
+        T, dm = x2d.shape
+        di = w_gate.shape[1]
+        out = torch.empty((T, di), device=x2d.device, dtype=x2d.dtype)
+        s, t = torch.empty_like(out), torch.empty_like(out)
+        with torch.cuda.device(x2d.device):
+            rc = _lib.load().fsw_forward_st(
+                x2d.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), out.data_ptr(), s.data_ptr(), t.data_ptr(),
+                T, dm, di, _code(x2d), _lib.FSW_ACC_F16 if fast_accum else _lib.FSW_ACC_F32, _stream(x2d))
+        _lib.check("fsw_forward_st", rc)
+        return out, s, t
     _require_cuda(x2d, w_gate, w_up)
     T, dm = x2d.shape
     di = w_gate.shape[1]
@@ -175,6 +190,36 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         )
     _lib.check("fsw_gemm", rc)
     return c
+
+
+def grad_input_fused(dout: torch.Tensor, s: torch.Tensor, t: torch.Tensor, w_gate: torch.Tensor,
+                     w_up: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(dX, dg, du) in one launch from dout and the factors saved by
+    ``forward(save_factors=True)``: dg = dout * t and du = dout * s are produced inside
+    the dX GEMM and also written out for the weight-gradient GEMM."""
+    _require_cuda(dout, s, t, w_gate, w_up)
+    T, di = dout.shape
+    dm = w_gate.shape[0]
+    dx = torch.empty((T, dm), device=dout.device, dtype=dout.dtype)
+    dg, du = torch.empty_like(dout), torch.empty_like(dout)
+    with torch.cuda.device(dout.device):
+        rc = _lib.load().fsw_backward_dx_fused(
+            dout.data_ptr(), s.data_ptr(), t.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), dx.data_ptr(),
+            dg.data_ptr(), du.data_ptr(), T, dm, di, _code(dout), _stream(dout))
+    _lib.check("fsw_backward_dx_fused", rc)
+    return dx, dg, du
+
+
+def gate_grad_from_factors(dout: torch.Tensor, s: torch.Tensor, t: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(dg, du) = (dout * t, dout * s) as a kernel of its own."""
+    _require_cuda(dout, s, t)
+    dg, du = torch.empty_like(dout), torch.empty_like(dout)
+    with torch.cuda.device(dout.device):
+        rc = _lib.load().fsw_backward_elementwise_st(
+            dout.data_ptr(), s.data_ptr(), t.data_ptr(), dg.data_ptr(), du.data_ptr(), dout.numel(),
+            _code(dout), _stream(dout))
+    _lib.check("fsw_backward_elementwise_st", rc)
+    return dg, du
 
 
 def _ptr_array(ptrs):

@@ -112,6 +112,14 @@ static int ensure_device(DeviceInfo** out) {
   int dev = 0;
   FSW_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return fail(FSW_EINVAL, "device index %d out of range", dev);
+  // The tensor-map encoder is a driver call and needs the device's context current on
+  // THIS thread; a thread that has made no runtime call with side effects yet (an
+  // autograd worker whose first call lands here) has none.  cudaSetDevice binds it.
+  static thread_local int t_bound_device = -1;
+  if (t_bound_device != dev) {
+    FSW_CUDA(cudaSetDevice(dev));
+    t_bound_device = dev;
+  }
   std::lock_guard<std::mutex> lock(g_mu);
   DeviceInfo& d = g_dev[dev];
   if (!d.ready) {
@@ -142,6 +150,9 @@ static int ensure_device(DeviceInfo** out) {
     FSW_CUDA((prepare_mode<MODE_FWD, 2, 2>()));
     FSW_CUDA((prepare_mode<MODE_DX, 2, 2>()));
     FSW_CUDA((prepare_mode<MODE_DW, 2, 2>()));
+    FSW_CUDA((prepare_mode<MODE_DXG, 1, 1>()));
+    FSW_CUDA((prepare_mode<MODE_DXG, 2, 1>()));
+    FSW_CUDA((prepare_mode<MODE_DXG, 2, 2>()));
     FSW_CUDA((prepare_mode<MODE_NN, 1, 1>()));
     FSW_CUDA((prepare_mode<MODE_NT, 1, 1>()));
     FSW_CUDA((prepare_mode<MODE_TN, 1, 1>()));
@@ -446,7 +457,7 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   p.wait_limit_ns = (unsigned long long)g_opt.wait_limit_ms * 1000000ull;
   p.stall_producer = (int)g_opt.stall_producer;
   const int a_major = (MODE == MODE_DW || MODE == MODE_TN) ? MAJOR_MN : MAJOR_K;
-  const int b_major = (MODE == MODE_DX || MODE == MODE_NT) ? MAJOR_K : MAJOR_MN;
+  const int b_major = (MODE == MODE_DX || MODE == MODE_NT || MODE == MODE_DXG) ? MAJOR_K : MAJOR_MN;
   fill_operand_desc(a_major, &p.a_desc, &p.a_kadv);
   fill_operand_desc(b_major, &p.b_desc, &p.b_kadv);
   p.idesc = make_idesc(dtype, acc16, a_major, b_major, 128 * cg, 256);
@@ -516,7 +527,7 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
     int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
     // Split the last partial wave along K over all pairs when the caller gave a
     // workspace and the tail would otherwise idle most of the GPU.
-    constexpr int nseg = (MODE == MODE_DX) ? 2 : 1;
+    constexpr int nseg = (MODE == MODE_DX || MODE == MODE_DXG) ? 2 : 1;
     const long long ipt = (long long)nseg * p.num_k_blocks;
     p.sk_total_iters = 0;
     if (nsub == 2 && ws != nullptr && g_opt.split_k != 0 &&
@@ -663,6 +674,24 @@ __global__ void __launch_bounds__(256) gate_grad_kernel(const T* __restrict__ do
     const uint32_t a = pack2<T>(dgv, 0.f), b = pack2<T>(duv, 0.f);
     reinterpret_cast<unsigned short*>(dg)[i] = static_cast<unsigned short>(a & 0xFFFFu);
     reinterpret_cast<unsigned short*>(du)[i] = static_cast<unsigned short>(b & 0xFFFFu);
+  }
+}
+
+// dg = dout * t, du = dout * s from the activations saved by a forward with save_st:
+// two packed multiplies per pair, each rounding once.
+template <typename T>
+__global__ void __launch_bounds__(256) gate_grad_st_kernel(const uint4* __restrict__ dout,
+                                                          const uint4* __restrict__ s,
+                                                          const uint4* __restrict__ t, uint4* __restrict__ dg,
+                                                          uint4* __restrict__ du, int64_t nvec) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    const uint4 d = ld_stream(dout + v), a = ld_stream(s + v), b = ld_stream(t + v);
+    uint4 og, ou;
+    og.x = mul2<T>(d.x, b.x); og.y = mul2<T>(d.y, b.y); og.z = mul2<T>(d.z, b.z); og.w = mul2<T>(d.w, b.w);
+    ou.x = mul2<T>(d.x, a.x); ou.y = mul2<T>(d.y, a.y); ou.z = mul2<T>(d.z, a.z); ou.w = mul2<T>(d.w, a.w);
+    dg[v] = og;
+    du[v] = ou;
   }
 }
 
@@ -819,9 +848,27 @@ int fsw_forward(const void* x, const void* w_gate, const void* w_up, void* out, 
   return fsw_forward_ws(x, w_gate, w_up, out, g, u, T, dm, di, nullptr, 0, dtype, accum, stream);
 }
 
+static int forward_impl(const void* x, const void* w_gate, const void* w_up, void* out, void* g, void* u,
+                        int64_t T, int64_t dm, int64_t di, void* workspace, int64_t workspace_bytes,
+                        int dtype, int accum, void* stream, int save_st);
+
 int fsw_forward_ws(const void* x, const void* w_gate, const void* w_up, void* out, void* g, void* u,
                    int64_t T, int64_t dm, int64_t di, void* workspace, int64_t workspace_bytes,
                    int dtype, int accum, void* stream) {
+  return forward_impl(x, w_gate, w_up, out, g, u, T, dm, di, workspace, workspace_bytes, dtype, accum,
+                      stream, 0);
+}
+
+int fsw_forward_st(const void* x, const void* w_gate, const void* w_up, void* out, void* s, void* t,
+                   int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream) {
+  if (!s || !t) return fail(FSW_EINVAL, "s and t are required");
+  // (the second pass of a split last wave only knows the g / u form, so no workspace here)
+  return forward_impl(x, w_gate, w_up, out, s, t, T, dm, di, nullptr, 0, dtype, accum, stream, 1);
+}
+
+static int forward_impl(const void* x, const void* w_gate, const void* w_up, void* out, void* g, void* u,
+                        int64_t T, int64_t dm, int64_t di, void* workspace, int64_t workspace_bytes,
+                        int dtype, int accum, void* stream, int save_st) {
   int rc = check_common(T, dm, di, dtype, accum);
   if (rc != FSW_OK) return rc;
   if (T == 0) return FSW_OK;  // nothing to compute; empty tensors may have NULL storage
@@ -846,6 +893,7 @@ int fsw_forward_ws(const void* x, const void* w_gate, const void* w_up, void* ou
   p.N = (int)di;
   p.num_k_blocks = (int)((dm + 63) / 64);
   p.store_gu = g != nullptr;
+  p.save_st = save_st;
   p.c0_ptr = g;
   p.c1_ptr = u;
   p.c2_ptr = out;
@@ -883,6 +931,68 @@ int fsw_backward_elementwise(const void* dout, const void* g, const void* u, voi
         static_cast<const __half*>(u), static_cast<__half*>(dg), static_cast<__half*>(du), numel);
   FSW_CUDA(cudaGetLastError());
   return FSW_OK;
+}
+
+int fsw_backward_elementwise_st(const void* dout, const void* s, const void* t, void* dg, void* du,
+                                int64_t numel, int dtype, void* stream) {
+  if (dtype != FSW_BF16 && dtype != FSW_FP16) return fail(FSW_EINVAL, "unknown dtype %d", dtype);
+  if (numel < 0 || (numel & 7)) return fail(FSW_EINVAL, "numel must be a non-negative multiple of 8");
+  if (numel == 0) return FSW_OK;
+  if (!dout || !s || !t || !dg || !du) return fail(FSW_EINVAL, "NULL pointer");
+  if (!aligned16(dout) || !aligned16(s) || !aligned16(t) || !aligned16(dg) || !aligned16(du))
+    return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
+  DeviceInfo* d = nullptr;
+  int rc = ensure_device(&d);
+  if (rc != FSW_OK) return rc;
+  const int64_t nvec = numel >> 3;
+  int64_t blocks = (nvec + 255) / 256;
+  const int64_t cap = (int64_t)d->sm_count * 32;
+  if (blocks > cap) blocks = cap;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FSW_BF16)
+    gate_grad_st_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const uint4*>(dout), static_cast<const uint4*>(s), static_cast<const uint4*>(t),
+        static_cast<uint4*>(dg), static_cast<uint4*>(du), nvec);
+  else
+    gate_grad_st_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(
+        static_cast<const uint4*>(dout), static_cast<const uint4*>(s), static_cast<const uint4*>(t),
+        static_cast<uint4*>(dg), static_cast<uint4*>(du), nvec);
+  FSW_CUDA(cudaGetLastError());
+  return FSW_OK;
+}
+
+// dX GEMM with the gate-gradient step inside: the A tiles dout * t and dout * s are
+// produced by the kernel's own warps; dg and du are also written out for the dW GEMM.
+int fsw_backward_dx_fused(const void* dout, const void* s, const void* t, const void* w_gate,
+                          const void* w_up, void* dx, void* dg, void* du, int64_t T, int64_t dm,
+                          int64_t di, int dtype, void* stream) {
+  int rc = check_common(T, dm, di, dtype, FSW_ACC_F32);
+  if (rc != FSW_OK) return rc;
+  if (T == 0) return FSW_OK;
+  if (!dout || !s || !t || !w_gate || !w_up || !dx || !dg || !du) return fail(FSW_EINVAL, "NULL pointer");
+  if (!aligned16(dout) || !aligned16(s) || !aligned16(t) || !aligned16(w_gate) || !aligned16(w_up) ||
+      !aligned16(dx) || !aligned16(dg) || !aligned16(du))
+    return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
+  DeviceInfo* d = nullptr;
+  if ((rc = ensure_device(&d)) != FSW_OK) return rc;
+  const TileChoice tc = choose_tiles(MODE_DX, T, dm, d);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  // A has no tensor map (the warps read dout, s, t with plain loads); the maps of B are MODE_DX's
+  if ((rc = make_map(&p.b0, w_gate, dtype, di, dm, 256 / tc.cg, "w_gate")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.b1, w_up, dtype, di, dm, 256 / tc.cg, "w_up")) != FSW_OK) return rc;
+  p.a0 = p.a1 = p.b0;
+  p.c0_ptr = dx;
+  p.M = (int)T;
+  p.N = (int)dm;
+  p.num_k_blocks = (int)((di + 63) / 64);
+  p.gg_dout = dout;
+  p.gg_s = s;
+  p.gg_t = t;
+  p.gg_dg = dg;
+  p.gg_du = du;
+  p.gg_k = (int)di;
+  return run_gemm<MODE_DXG>(p, (int)T, dtype, false, static_cast<cudaStream_t>(stream), d, tc);
 }
 
 int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const void* w_up, void* dx,

@@ -6,6 +6,12 @@
 //   MODE_DX  : dX = dg @ W_gate^T + du @ W_up^T      (A K-major, B K-major)
 //              one accumulator, the K loop runs over both products
 //   MODE_DW  : [dW_gate | dW_up] = x^T @ [dg | du]   (A MN-major, B MN-major)
+//   MODE_DXG : MODE_DX with the gate-gradient step inside: its A tiles dg = dout * t and
+//              du = dout * s are not loaded but produced by the epilogue warps from
+//              dout and the activations s = silu(g), t = u * silu'(g) that the forward
+//              saved (GemmParams::save_st), straight into the swizzled operand stage;
+//              the tiles of the first column of tiles also write dg and du out, for the
+//              dW GEMM
 // and, for the projection that follows SwiGLU in an MLP block, three plain
 // single-product GEMMs C = op(A) @ op(B) on row-major arrays:
 //   MODE_NN  : A (M,K) @ B (K,N)      (A K-major,  B MN-major)
@@ -45,7 +51,7 @@
 
 namespace fsw {
 
-enum : int { MODE_FWD = 0, MODE_DX = 1, MODE_DW = 2, MODE_NN = 3, MODE_NT = 4, MODE_TN = 5 };
+enum : int { MODE_FWD = 0, MODE_DX = 1, MODE_DW = 2, MODE_NN = 3, MODE_NT = 4, MODE_TN = 5, MODE_DXG = 6 };
 enum : int { MAJOR_K = 0, MAJOR_MN = 1 };
 
 // Codes written to the status word when a bounded wait gives up.
@@ -55,6 +61,8 @@ enum : uint32_t {
   WAIT_MMA_FULL = 2,
   WAIT_MMA_TMEM_EMPTY = 3,
   WAIT_EPI_TMEM_FULL = 4,
+  WAIT_XFORM_EMPTY = 6,   // (5 is WAIT_PEER_PARTIALS, below)
+  WAIT_MMA_XFORM = 7,
 };
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // default limit per wait: 2 s
@@ -73,6 +81,12 @@ struct GemmParams {
   int num_m_tiles, num_n_tiles, group_m;
   int num_k_blocks;        // 64-wide K blocks per product
   int store_gu;            // MODE_FWD: also write g and u
+  int save_st;             // MODE_FWD: write s = silu(g) and t = u * silu'(g) in their place
+  // MODE_DXG: dout, s, t (T x di, row-major, read with plain loads) and the dg / du
+  // arrays that the tiles of column 0 write
+  const void *gg_dout, *gg_s, *gg_t;
+  void *gg_dg, *gg_du;
+  int gg_k;                // di: row length of the five arrays above
   int l2_a, l2_b;          // L2 eviction priority of A / B loads: 0 normal, 1 first, 2 last
   int l2_out;              // same for the forward's output stores
   uint32_t* status;        // device status word (0 = ok)
@@ -160,7 +174,9 @@ template <int MODE, int CG, int NSUB>
 struct TileCfg {
   static_assert(NSUB == 1 || (NSUB == 2 && CG == 2), "512-column tiles need a CTA pair");
   static constexpr int A_MAJOR = (MODE == MODE_DW || MODE == MODE_TN) ? MAJOR_MN : MAJOR_K;
-  static constexpr int B_MAJOR = (MODE == MODE_DX || MODE == MODE_NT) ? MAJOR_K : MAJOR_MN;
+  static constexpr int B_MAJOR = (MODE == MODE_DX || MODE == MODE_NT || MODE == MODE_DXG) ? MAJOR_K : MAJOR_MN;
+  // the A operand is written by the epilogue warps instead of TMA
+  static constexpr bool A_BY_WARPS = (MODE == MODE_DXG);
   // dual: the accumulator columns of a region are [128 from b0 | 128 from b1]
   static constexpr bool DUAL_B = (MODE == MODE_FWD || MODE == MODE_DW);
   static constexpr int BM = 128;          // accumulator rows per CTA
@@ -176,14 +192,14 @@ struct TileCfg {
   static_assert(EPI_WARPS == 4 || EPI_WARPS == 8, "4 or 8 epilogue warps");
   static constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows x 64 16-bit columns per warp
   static constexpr int EPI_BYTES = EPI_WARPS * EPI_BUF_BYTES;
-  static constexpr int BAR_BYTES = 256;
+  static constexpr int BAR_BYTES = 512;
   // as many operand stages as fit beside the epilogue staging
   static constexpr int STAGES = (kSmemBudget - 1024 - BAR_BYTES - EPI_BYTES) / STAGE_BYTES;
   static_assert(STAGES >= 2 && STAGES <= 12, "unexpected stage count");
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int NSEG = (MODE == MODE_DX) ? 2 : 1;
+  static constexpr int NSEG = (MODE == MODE_DX || MODE == MODE_DXG) ? 2 : 1;
   // Output columns covered by one accumulator region / one tile, per output tensor.
   static constexpr int REGION_N = DUAL_B ? 128 : 256;
   static constexpr int TILE_N = REGION_N * NSUB;
@@ -515,11 +531,29 @@ __device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& 
     const uint32_t* pu = &U[c * 16];
     const int col = n0 + jb_begin * 64 + c * 32;
     const bool in_range = rows_ok && col < p.N;
+    // silu(g) rounded to the 16-bit type: a factor of out, and what is saved in place
+    // of g when the backward wants s = silu(g) and t = u * silu'(g) (save_st)
+    uint32_t ps[16], pt[16];
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {
+      float g0, g1;
+      unpack2<T>(pg[q], g0, g1);
+      const float s0 = sigmoid_f32(g0), s1 = sigmoid_f32(g1);
+      const float silu0 = g0 * s0, silu1 = g1 * s1;
+      ps[q] = pack2<T>(silu0, silu1);
+      if (p.save_st)  // silu'(g) = sg + silu * (1 - sg), rounded, times u, rounded
+        pt[q] = mul2<T>(pu[q], pack2<T>(fmaf(silu0, 1.0f - s0, s0), fmaf(silu1, 1.0f - s1, s1)));
+    }
     if (p.store_gu) {
       if (e.lane == 0) ptx::tma_store_wait_read<0>();
       __syncwarp();
-      stage_rows64(buf0, e.lane, *reinterpret_cast<const uint32_t(*)[16]>(pg));
-      stage_rows64(buf1, e.lane, *reinterpret_cast<const uint32_t(*)[16]>(pu));
+      if (p.save_st) {
+        stage_rows64(buf0, e.lane, ps);
+        stage_rows64(buf1, e.lane, pt);
+      } else {
+        stage_rows64(buf0, e.lane, *reinterpret_cast<const uint32_t(*)[16]>(pg));
+        stage_rows64(buf1, e.lane, *reinterpret_cast<const uint32_t(*)[16]>(pu));
+      }
       ptx::fence_proxy_async_smem();
       __syncwarp();
       if (e.lane == 0 && in_range) {
@@ -530,11 +564,7 @@ __device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& 
     }
     uint32_t po[16];
 #pragma unroll
-    for (int q = 0; q < 16; ++q) {
-      float g0, g1;
-      unpack2<T>(pg[q], g0, g1);
-      po[q] = mul2<T>(pack2<T>(g0 * sigmoid_f32(g0), g1 * sigmoid_f32(g1)), pu[q]);
-    }
+    for (int q = 0; q < 16; ++q) po[q] = mul2<T>(ps[q], pu[q]);
     if (e.lane == 0) ptx::tma_store_wait_read<0>();
     __syncwarp();
     stage_rows64(buf0, e.lane, po);
@@ -634,6 +664,59 @@ __device__ __forceinline__ void drain_partial(const GemmParams& p, int lane, uin
   }
 }
 
+// ------------------------------------------ A tiles produced by the warps --
+// MODE_DXG.  One K block of the A operand is 128 rows x 64 elements = 1024 chunks of
+// 16 bytes; the EPI_WARPS * 32 threads take chunks tid, tid + 256, ... (8 lanes cover
+// one row's 128 bytes, so global accesses are whole 128-byte segments).  The chunk of
+// row r, 16-byte column c goes to byte r * 128 + ((c ^ (r & 7)) << 4) of the stage:
+// the 128-byte swizzle that TMA would have written and the MMA descriptor expects.
+struct GateGradTile {
+  uint4 d[4], a[4];  // dout and the saved activation (t or s) for this thread's four chunks
+};
+__device__ __forceinline__ uint4 ldg_nc16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+template <int THREADS>
+__device__ __forceinline__ void gate_grad_issue(const GemmParams& p, int tid, int m0, int k0, bool second_is_s,
+                                                GateGradTile& g) {
+  const char* second = static_cast<const char*>(second_is_s ? p.gg_s : p.gg_t);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int chunk = tid + THREADS * i;
+    const int row = m0 + (chunk >> 3), col = k0 + (chunk & 7) * 8;
+    if (row < p.M && col < p.gg_k) {  // gg_k is a multiple of 8: a chunk is all in or all out
+      const size_t off = (static_cast<size_t>(row) * p.gg_k + col) * 2;
+      g.d[i] = ldg_nc16(static_cast<const char*>(p.gg_dout) + off);
+      g.a[i] = ldg_nc16(second + off);
+    } else {
+      g.d[i] = make_uint4(0u, 0u, 0u, 0u);
+      g.a[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+}
+template <typename T, int THREADS>
+__device__ __forceinline__ void gate_grad_write(const GemmParams& p, int tid, int m0, int k0, uint32_t a_dst,
+                                                const GateGradTile& g, void* grad_out) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int chunk = tid + THREADS * i;
+    const int r = chunk >> 3, c = chunk & 7;
+    const uint32_t w0 = mul2<T>(g.d[i].x, g.a[i].x), w1 = mul2<T>(g.d[i].y, g.a[i].y);
+    const uint32_t w2 = mul2<T>(g.d[i].z, g.a[i].z), w3 = mul2<T>(g.d[i].w, g.a[i].w);
+    ptx::st_shared_v4(a_dst + r * 128u + ((c ^ (r & 7)) << 4), w0, w1, w2, w3);
+    if (grad_out != nullptr) {
+      const int row = m0 + r, col = k0 + c * 8;
+      if (row < p.M && col < p.gg_k)
+        ptx::st_global_v4(static_cast<char*>(grad_out) + (static_cast<size_t>(row) * p.gg_k + col) * 2, w0, w1,
+                          w2, w3);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ kernel --
 template <int MODE, int CG, int NSUB, typename T, bool ACC16>
 __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
@@ -652,6 +735,8 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  // A_BY_WARPS: "the warps have written stage s's A tile" (all epilogue warps of both CTAs arrive)
+  auto xf_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 5 + s); };
   const uint32_t misc_off = (bar_base - smem_base) + 8u * (2 * STAGES + 4);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + misc_off);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + misc_off + 4);
@@ -677,6 +762,8 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
       ptx::mbar_init(tfull_bar(a), 1);
       ptx::mbar_init(tempty_bar(a), C::TEMPTY_COUNT);
     }
+    if (C::A_BY_WARPS)
+      for (int s = 0; s < STAGES; ++s) ptx::mbar_init(xf_bar(s), C::EPI_WARPS * CG);
     *abort_flag = 0u;
     ptx::fence_mbar_init();
   }
@@ -750,7 +837,9 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
             if (CG == 2) fb = ptx::mapa(fb, 0);
             if (cta_rank == 0)
               ptx::mbar_arrive_expect_tx(full_bar(s),
-                                         CG * (FSW_DBG_SKIP_B_LOADS ? C::A_BYTES : C::STAGE_BYTES));
+                                         CG * (FSW_DBG_SKIP_B_LOADS ? C::A_BYTES
+                                               : C::A_BY_WARPS      ? C::B_BYTES
+                                                                    : C::STAGE_BYTES));
             auto load_pol = [&](uint32_t dst, const CUtensorMap* tm, int x, int y, uint64_t pol) {
               if (CG == 2)
                 ptx::tma_load_2d_pair(dst, tm, fb, x, y, pol);
@@ -764,7 +853,9 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
               load_pol(dst, tm, x, y, pol_b);
             };
             // ---- A tile: 128 rows x 64 k
-            if (C::A_MAJOR == MAJOR_K) {
+            if (C::A_BY_WARPS) {
+              // written by the epilogue warps (see the transform loop below)
+            } else if (C::A_MAJOR == MAJOR_K) {
               load_a(a_dst, (MODE == MODE_DX && seg == 1) ? &p.a1 : &p.a0, k0, m0);
             } else {
 #pragma unroll
@@ -829,6 +920,7 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
         for (int it = 0; it < iters; ++it) {
           if (FSW_PROFILE) prof_t0 = clock64();
           if (!FSW_DBG_SKIP_LOADS) ok = bounded_wait_thread(full_bar(s), ph, ctl, WAIT_MMA_FULL);
+          if (ok && C::A_BY_WARPS) ok = bounded_wait_thread(xf_bar(s), ph, ctl, WAIT_MMA_XFORM);
           if (FSW_PROFILE) prof_full += clock64() - prof_t0;
           if (!ok) break;
           ptx::tc_fence_after_sync();
@@ -887,11 +979,61 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
     int a = 0;
     uint32_t aph = 0;
     bool ok = true;
+    int xs = 0;        // A_BY_WARPS: stage and phase of the next A tile the warps write
+    uint32_t xph = 0;
     long long prof_wait = 0, prof_drain = 0, prof_t0 = 0, prof_tiles = 0;
     WorkItem w;
     for (int idx = 0; ok && next_work(p, C::NSEG * num_kb, cluster_id, num_clusters, idx, w); ++idx) {
       e.row0 = w.m_tile * C::TILE_M + cta_rank * C::BM + q * 32;
       const int n0 = w.n_tile * C::TILE_N;
+      if (C::A_BY_WARPS) {
+        // Produce this item's A tiles: dg = dout * t for the first num_kb iterations,
+        // du = dout * s for the rest.  Loads run kPrefetch iterations ahead of their use.
+        constexpr int kThreads = C::EPI_WARPS * 32;
+        constexpr int kPrefetch = 2;
+        const int tid = ew * 32 + lane;
+        const int m0 = w.m_tile * C::TILE_M + cta_rank * C::BM;
+        const bool write_out = (w.n_tile == 0);  // one tile per row of tiles emits dg / du for the dW GEMM
+        GateGradTile gt[kPrefetch];
+#pragma unroll
+        for (int j = 0; j < kPrefetch; ++j) {
+          const int it = w.it0 + j;
+          if (it < w.it1)
+            gate_grad_issue<kThreads>(p, tid, m0, (it >= num_kb ? it - num_kb : it) * C::BK, it >= num_kb, gt[j]);
+        }
+        for (int base = w.it0; base < w.it1 && ok; base += kPrefetch) {
+#pragma unroll
+          for (int j = 0; j < kPrefetch; ++j) {
+            const int it = base + j;
+            if (it < w.it1 && ok) {
+              const bool second = it >= num_kb;
+              const int k0 = (second ? it - num_kb : it) * C::BK;
+              ok = bounded_wait_warp(empty_bar(xs), xph ^ 1u, ctl, WAIT_XFORM_EMPTY);
+              if (ok) {
+                gate_grad_write<T, kThreads>(p, tid, m0, k0, smem_base + xs * C::STAGE_BYTES, gt[j],
+                                             write_out ? (second ? p.gg_du : p.gg_dg) : nullptr);
+                const int nx = it + kPrefetch;
+                if (nx < w.it1)
+                  gate_grad_issue<kThreads>(p, tid, m0, (nx >= num_kb ? nx - num_kb : nx) * C::BK, nx >= num_kb,
+                                            gt[j]);
+                ptx::fence_proxy_async_smem();  // the MMA reads the tile through the async proxy
+                __syncwarp();
+                if (lane == 0) {
+                  if (CG == 2)
+                    ptx::mbar_arrive_cluster(ptx::mapa(xf_bar(xs), 0));
+                  else
+                    ptx::mbar_arrive(xf_bar(xs));
+                }
+                if (++xs == STAGES) {
+                  xs = 0;
+                  xph ^= 1u;
+                }
+              }
+            }
+          }
+        }
+        if (!ok) break;
+      }
       if (FSW_PROFILE) prof_t0 = clock64();
       ok = bounded_wait_warp(tfull_bar(NSUB == 2 ? 0 : a), aph, ctl, WAIT_EPI_TMEM_FULL);
       if (FSW_PROFILE) {

@@ -17,6 +17,7 @@ from . import _autograd
 class FastAccumFusedSwiGLU(Function):
     fast_accum = True
     recompute_activations = False  # see FusedSwiGLU.recompute_activations
+    fused_gate_grad = False        # see FusedSwiGLU.fused_gate_grad
 
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float16)
@@ -24,7 +25,8 @@ class FastAccumFusedSwiGLU(Function):
         assert input.dtype == torch.float16, "Expected torch.float16 inputs and weights."
         ctx.fast_accum = bool(FastAccumFusedSwiGLU.fast_accum)
         return _autograd.swiglu_forward(ctx, input, weight_gate, weight_up, fast_accum=ctx.fast_accum,
-                                        recompute=bool(FastAccumFusedSwiGLU.recompute_activations))
+                                        recompute=bool(FastAccumFusedSwiGLU.recompute_activations),
+                                        fused_gate_grad=bool(FastAccumFusedSwiGLU.fused_gate_grad))
 
     @staticmethod
     @torch.amp.custom_bwd(device_type="cuda")

@@ -130,6 +130,34 @@ int fsw_backward(const void* dout, const void* x, const void* w_gate, const void
                  int accum, void* stream);
 
 /*
+ * The gate-gradient step inside the dX GEMM ("dg = dout*u*silu'(g) and du = dout*silu(g)
+ * computed on-chip").  Replaces elementwise_backward (kernels_bf16.py:210-255) and the
+ * two matmuls of swiglu.py:45 by ONE launch.
+ *
+ * fsw_forward_st is fsw_forward that saves, in place of g and u, the two factors the
+ * backward needs: s = round(silu(g)) and t = round(u * round(silu'(g))), both from
+ * the 16-bit g and u.  Then dg = round(dout * t) and du = round(dout * s): one
+ * multiply each (the reference rounds dout*u first and multiplies by silu'(g) second,
+ * kernels_bf16.py:230-231; the two orders differ by one rounding of a 16-bit product).
+ *
+ * fsw_backward_dx_fused computes dx = dg @ w_gate^T + du @ w_up^T without reading dg
+ * or du: the kernel's epilogue warps load dout, t and s tiles, multiply, and write the
+ * products straight into the swizzled shared-memory operand stage of the tensor-core
+ * pipeline.  The tiles of the first column of output tiles also store dg and du (T, di)
+ * for fsw_backward_dw, which follows.  fp32 accumulation.
+ *
+ * fsw_backward_elementwise_st is the same dg/du step as a kernel of its own (numel a
+ * multiple of 8).
+ */
+int fsw_forward_st(const void* x, const void* w_gate, const void* w_up, void* out, void* s, void* t,
+                   int64_t T, int64_t dm, int64_t di, int dtype, int accum, void* stream);
+int fsw_backward_dx_fused(const void* dout, const void* s, const void* t, const void* w_gate,
+                          const void* w_up, void* dx, void* dg, void* du, int64_t T, int64_t dm,
+                          int64_t di, int dtype, void* stream);
+int fsw_backward_elementwise_st(const void* dout, const void* s, const void* t, void* dg, void* du,
+                                int64_t numel, int dtype, void* stream);
+
+/*
  * dX reduced across GPUs inside the kernels (no counterpart in the reference, which
  * is single-GPU).  With d_intermediate split over `world` ranks (2..8) every rank's
  * dX GEMM yields a partial sum of the whole (T, dm) gradient.  Rank r owns rows

@@ -378,6 +378,77 @@ def test_dw_beside_a_collective_in_two_parts_equals_one_launch(monkeypatch):
     assert torch.equal(got_g, want_g) and torch.equal(got_u, want_u)
 
 
+# ------------------------------------- gate gradient inside the dX GEMM --
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("T,dm,di", [(1000, 320, 1096), (2048, 512, 1536), (4224, 512, 2304), (130, 8, 8)])
+def test_gate_gradient_inside_the_dx_gemm(T, dm, di, dtype):
+    """The forward that saves s = silu(g) and t = u*silu'(g), and the dX GEMM whose warps
+    produce dg = dout*t and du = dout*s on-chip: out is unchanged; s and t follow their
+    formulas; the dg/du the kernel writes out are exactly dout*t and dout*s; dX is exactly
+    the plain dX GEMM of those dg/du (same operand values, same accumulation order); and
+    against the three-kernel path everything agrees to a rounding (the products are
+    associated the other way round).  Ragged T, d_model and d_intermediate included."""
+    from fusedswiglu_b200 import _launch, _lib
+
+    inp = orc.make_inputs(1, T, dm, di, dtype, seed=T + di, dout_std=0.5)
+    x, wg, wu = dev(inp["x"].reshape(T, dm), dtype), dev(inp["w_gate"], dtype), dev(inp["w_up"], dtype)
+    dout = dev(inp["dout"].reshape(T, di), dtype)
+    out0, g, u = _launch.forward(x, wg, wu, split_k=False)
+    out1, s, t = _launch.forward(x, wg, wu, save_factors=True)
+    assert torch.equal(out0, out1)
+    gf = host(g).astype(np.float32)
+    s_ref = orc.round16(orc.silu_f32(gf), dtype)
+    t_ref = orc.round16(host(u) * orc.round16(orc.silu_grad_f32(gf), dtype), dtype)
+    for name, got, want in (("s", s, s_ref), ("t", t, t_ref)):
+        assert orc.rel_error(host(got), want) < 1e-3, name
+        assert np.mean(orc.to_bits(host(got), dtype) != orc.to_bits(want, dtype)) < 0.02, name  # fast sigmoid
+    dx, dg, du = _launch.grad_input_fused(dout, s, t, wg, wu)
+    dg2, du2 = _launch.gate_grad_from_factors(dout, s, t)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert torch.equal(dg, (dout.float() * t.float()).to(dout.dtype)) and torch.equal(dg, dg2)
+    assert torch.equal(du, (dout.float() * s.float()).to(dout.dtype)) and torch.equal(du, du2)
+    assert torch.equal(dx, _launch.grad_input(dg, du, wg, wu, split_k=False))
+    # against the reference-order path
+    dg0, du0 = _launch.gate_grad(dout, g, u)
+    dx0 = _launch.grad_input(dg0, du0, wg, wu, split_k=False)
+    assert torch.equal(du, du0)                      # du = dout * round(silu(g)) in both
+    for name, a, b in (("dg", dg, dg0), ("dx", dx, dx0)):
+        e = rel_error(a, b)
+        print(f"fused gate gradient {dtype} T={T} {name}: rel_fro vs three-kernel path {e:.3e}")
+        assert e < (4e-3 if dtype == "bf16" else 6e-4), (name, e)
+
+
+def test_fused_gate_gradient_mode_of_the_autograd_function():
+    """FusedSwiGLU.fused_gate_grad = True on shapes of the reference's backward test,
+    with its tolerance, against the PyTorch SwiGLU + autograd."""
+    from fused_swiglu import FusedSwiGLU
+
+    torch.manual_seed(0)
+    worst = {}
+    FusedSwiGLU.fused_gate_grad = True
+    try:
+        for bs, sq, dm, di in [(1, 64, 64, 64), (2, 128, 256, 512), (3, 192, 512, 1024), (4, 256, 1024, 2048),
+                               (2, 512, 2048, 4096)]:
+            x, wg, wu = make_input_weights(bs, sq, dm, di)
+            dy = 0.1 * torch.randn(bs, sq, di, device="cuda", dtype=torch.bfloat16)
+            x.requires_grad_(True), wg.requires_grad_(True), wu.requires_grad_(True)
+            out = FusedSwiGLU.apply(x, wg, wu)
+            out.backward(dy)
+            got = {"out": out.detach(), "dx": x.grad, "dw_gate": wg.grad, "dw_up": wu.grad}
+            xr, wgr, wur = (t.detach().clone().requires_grad_(True) for t in (x, wg, wu))
+            ref = orc.swiglu_ref_torch(xr, wgr, wur)
+            ref.backward(dy)
+            want = {"out": ref.detach(), "dx": xr.grad, "dw_gate": wgr.grad, "dw_up": wur.grad}
+            for k in got:
+                e = rel_error(got[k], want[k])
+                worst[k] = max(worst.get(k, 0.0), e)
+                assert e < BFLOAT16_MAX_TOL, (bs, sq, dm, di, k, e)
+    finally:
+        FusedSwiGLU.fused_gate_grad = False
+    print("fused gate gradient, worst rel error per tensor:", worst)
+
+
 # ------------------------------------------------------------- fp16 paths --
 @pytest.mark.parametrize("d_model", [1024, 2048])
 def test_fp16_fast_accum_against_fp32_accum(d_model):
