@@ -89,7 +89,7 @@ def parse_args():
                     help="fp16 workloads: accumulate in fp32 instead of the fp16 accumulator")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="library tuning knob passed to fsw_set_option, e.g. --opt group_m=16 (repeatable)")
-    ap.add_argument("--only", default=None, choices=["fwd", "ew", "dx", "dw", "fwdst", "dxf"],
+    ap.add_argument("--only", default=None, choices=["fwd", "ew", "dx", "dw", "fwdst", "dxf", "mlp"],
                     help="launch only this kernel in each step (for profiling one kernel); prints no bench line")
     ap.add_argument("--shard-of", type=int, default=1, metavar="N",
                     help="with --only on one GPU: time rank 0's 1/N column shard of the workload")
@@ -573,6 +573,47 @@ def run_ours(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.only == "mlp":
+        # The whole MLP block (SwiGLU + down projection, forward + backward) on this
+        # library against torch's (cuBLAS + eager elementwise) on the same GPU, alternating.
+        from fusedswiglu_b200.mlp import FusedSwiGLUMLP
+
+        xm = x.detach().clone().requires_grad_(True)
+        wgm, wum = (w_.detach().clone().requires_grad_(True) for w_ in (wg, wu))
+        wdm = (torch.randn(di_local, dm, device=dev, dtype=tdt, generator=g) / di_local ** 0.5).requires_grad_(True)
+        dy = torch.randn(bs, sq, dm, device=dev, dtype=tdt, generator=g)
+
+        def ours():
+            xm.grad = wgm.grad = wum.grad = wdm.grad = None
+            FusedSwiGLUMLP.apply(xm, wgm, wum, wdm).backward(dy)
+
+        def lib():
+            xm.grad = wgm.grad = wum.grad = wdm.grad = None
+            ((torch.nn.functional.silu(xm @ wgm) * (xm @ wum)) @ wdm).backward(dy)
+
+        t0 = time.time()
+        while time.time() - t0 < args.preheat:
+            ours()
+            torch.cuda.synchronize()
+        res = {"this_library": [], "torch": []}
+        for _ in range(4):
+            for name, fn in (("this_library", ours), ("torch", lib)):
+                for _ in range(3):
+                    fn()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(K):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                res[name].append(e0.elapsed_time(e1) / K)
+        flops = 18.0 * T * dm * di_local
+        med = {k: sorted(v)[len(v) // 2] for k, v in res.items()}
+        print(json.dumps({"only": "mlp", "workload": args.workload, "flops_per_step": flops,
+                          "ms": med, "tflops": {k: flops / v / 1e9 for k, v in med.items()},
+                          "status": _lib.device_status()}), flush=True)
+        return
 
     if args.only:
         # Profiling aid: the other kernels run once to produce this kernel's inputs.

@@ -173,7 +173,7 @@ def grad_weights(
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = False,
-         fast_accum: bool = False) -> torch.Tensor:
+         fast_accum: bool = False, split_k: bool = True) -> torch.Tensor:
     """C = op(A) @ op(B) for contiguous 2-D 16-bit tensors: A (M,K) or, with trans_a,
     (K,M); B (K,N) or, with trans_b, (N,K).  fp32 accumulation unless fast_accum (fp16)."""
     _require_cuda(a, b)
@@ -183,12 +183,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
     Kb, N = (b.shape[1], b.shape[0]) if trans_b else b.shape
     assert K == Kb, f"Dimension mismatch. Expected inner sizes to agree, got {K} and {Kb}"
     c = torch.empty((M, N), device=a.device, dtype=a.dtype)
+    ws = _workspace(a) if split_k and M > 0 and K > 0 else None
     with torch.cuda.device(a.device):
-        rc = _lib.load().fsw_gemm(
-            a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, int(trans_a), int(trans_b), _code(a),
+        rc = _lib.load().fsw_gemm_ws(
+            a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, int(trans_a), int(trans_b),
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, _code(a),
             _lib.FSW_ACC_F16 if fast_accum else _lib.FSW_ACC_F32, _stream(a),
         )
-    _lib.check("fsw_gemm", rc)
+    _lib.check("fsw_gemm_ws", rc)
     return c
 
 

@@ -33,6 +33,7 @@ SIGNATURES = {
     "fsw_workspace_bytes": (c_int64, []),
     "fsw_backward": (c_int, [c_void_p] * 11 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_gemm": (c_int, [c_void_p] * 3 + [c_int64] * 3 + [c_int] * 4 + [c_void_p]),
+    "fsw_gemm_ws": (c_int, [c_void_p] * 3 + [c_int64] * 3 + [c_int, c_int, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "fsw_backward_static_scratch": (c_int, [c_void_p] * 9 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_debug_split_work": (c_int, [c_int] * 7 + [POINTER(c_int64), POINTER(c_int)]),
     "fsw_debug_decode_tile": (c_int, [c_int] * 4 + [POINTER(c_int), POINTER(c_int)]),

@@ -1284,6 +1284,12 @@ int fsw_debug_descriptors(int dtype, int accum, int a_major, int b_major, int m,
 // that follows SwiGLU in an MLP block and its two gradients.
 int fsw_gemm(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int trans_a,
              int trans_b, int dtype, int accum, void* stream) {
+  return fsw_gemm_ws(a, b, c, M, N, K, trans_a, trans_b, nullptr, 0, dtype, accum, stream);
+}
+
+int fsw_gemm_ws(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int trans_a,
+                int trans_b, void* workspace, int64_t workspace_bytes, int dtype, int accum,
+                void* stream) {
   if (dtype != FSW_BF16 && dtype != FSW_FP16) return fail(FSW_EINVAL, "unknown dtype %d", dtype);
   if (accum != FSW_ACC_F32 && !(accum == FSW_ACC_F16 && dtype == FSW_FP16))
     return fail(FSW_EINVAL, "bad accumulate mode %d for dtype %d", accum, dtype);
@@ -1309,7 +1315,7 @@ int fsw_gemm(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_
   if (!aligned16(a) || !aligned16(b) || !aligned16(c))
     return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
   const int mode = trans_a ? MODE_TN : (trans_b ? MODE_NT : MODE_NN);
-  const TileChoice tc = choose_tiles(mode, M, N, d);
+  const TileChoice tc = choose_tiles(mode, M, N, d, 0, workspace != nullptr);
   GemmParams p;
   memset(&p, 0, sizeof(p));
   // A: K-major -> rows of 64 k, 128 rows per box; MN-major -> 64 m x 64 k boxes
@@ -1327,9 +1333,9 @@ int fsw_gemm(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_
   p.N = (int)N;
   p.num_k_blocks = (int)((K + 63) / 64);
   const bool acc16 = accum == FSW_ACC_F16;
-  if (mode == MODE_NN) return run_gemm<MODE_NN>(p, (int)M, dtype, acc16, st, d, tc);
-  if (mode == MODE_NT) return run_gemm<MODE_NT>(p, (int)M, dtype, acc16, st, d, tc);
-  return run_gemm<MODE_TN>(p, (int)M, dtype, acc16, st, d, tc);
+  if (mode == MODE_NN) return run_gemm<MODE_NN>(p, (int)M, dtype, acc16, st, d, tc, 0, workspace, workspace_bytes);
+  if (mode == MODE_NT) return run_gemm<MODE_NT>(p, (int)M, dtype, acc16, st, d, tc, 0, workspace, workspace_bytes);
+  return run_gemm<MODE_TN>(p, (int)M, dtype, acc16, st, d, tc, 0, workspace, workspace_bytes);
 }
 
 // ------------------------------------------------- backward without allocation --

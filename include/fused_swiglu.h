@@ -203,6 +203,10 @@ int fsw_wait_flags(void* flags, int n, uint32_t seq, void* stream);
  */
 int fsw_gemm(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int trans_a,
              int trans_b, int dtype, int accum, void* stream);
+/* The same with a workspace for the split of the last wave (see fsw_workspace_bytes). */
+int fsw_gemm_ws(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K, int trans_a,
+                int trans_b, void* workspace, int64_t workspace_bytes, int dtype, int accum,
+                void* stream);
 
 /*
  * fsw_backward for callers that have no scratch memory to give and may not
