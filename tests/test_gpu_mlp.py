@@ -78,3 +78,32 @@ def test_mlp_block_forward_backward(shape):
         e = rel(a, b)
         print(shape, name, e)
         assert e < TOL and e < EXPECTED, (name, e)
+
+
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn"])
+def test_plain_gemm_with_a_split_last_wave(layout):
+    """fsw_gemm_ws: 9 x 10 = 90 tiles are one wave of 74 plus 16 tiles whose K loops
+    (128 blocks) are divided over all SM pairs.  Deterministic, and within a rounding of
+    both the unsplit launch and a float64 product."""
+    from fusedswiglu_b200 import _launch, _lib
+
+    M, N, K = 2300, 5000, 8192
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, generator=gen)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16, generator=gen) / math.sqrt(K)
+    if layout == "nn":
+        run = lambda **kw: _launch.gemm(a, b, **kw)
+    elif layout == "nt":
+        bt = b.t().contiguous()
+        run = lambda **kw: _launch.gemm(a, bt, trans_b=True, **kw)
+    else:
+        at = a[:2296].t().contiguous()  # a row length must be a multiple of 8
+        run = lambda **kw: _launch.gemm(at, b, trans_a=True, **kw)
+    plain, s1, s2 = run(split_k=False), run(), run()
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    want = (a[:plain.shape[0]].double() @ b.double())
+    assert torch.equal(s1, s2)
+    assert int((s1 != plain).sum()) > 0          # the split did run
+    assert rel(s1, plain) < 1e-3
+    assert rel(s1, want) < 1.05 * rel(plain, want) + 1e-5

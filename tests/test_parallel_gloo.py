@@ -381,3 +381,29 @@ def test_peer_reducer_buffer_sets_alternate_and_never_overlap():
         assert len(words) == 4 * world
         assert PeerDxReducer.layout(1, world, 0, T, dm, esize)["set"] != PeerDxReducer.layout(2, world, 0, T, dm, esize)["set"]
         assert PeerDxReducer.layout(1, world, 0, T, dm, esize) == PeerDxReducer.layout(3, world, 0, T, dm, esize)
+
+
+def test_dw_columns_queued_before_the_peer_reduction():
+    """Host planning of PeerDxReducer: how the local dW GEMM is cut around the reduction.
+    Row-sharded mode has no gather to cover, so all of dW comes first; in replicated-x mode
+    the part after the reduction lasts about as long as the copy-engine gather and is a
+    whole number of tiles; with copy-engine scatter and a GEMM too short for two rounds of
+    copies each round gets half."""
+    from types import SimpleNamespace
+
+    from fusedswiglu_b200.parallel import DW_SPLIT_ALIGN, PeerDxReducer
+
+    def reducer(world, T, dm, mode="epilogue"):
+        return SimpleNamespace(world=world, T=T, dm=dm, rows=T // world, esize=2, scatter_mode=mode)
+
+    plan = PeerDxReducer.columns_before_reduction
+    for world, di_local in ((2, 7168), (4, 3584), (8, 1792)):
+        r = reducer(world, 32768, 4096)
+        assert plan(r, di_local, True) == di_local
+        first = plan(r, di_local, False)
+        assert 0 <= first < di_local and (di_local - first) % DW_SPLIT_ALIGN == 0
+    # the longer the GEMM relative to the gather, the larger the share that comes first
+    assert plan(reducer(2, 32768, 4096), 7168, False) / 7168 > plan(reducer(8, 32768, 4096), 1792, False) / 1792
+    # copy-engine scatter, 8 ranks: the GEMM (0.7 ms) is shorter than two rounds of copies
+    half = plan(reducer(8, 32768, 4096, "copy"), 1792, False)
+    assert half == (1792 // 2) // DW_SPLIT_ALIGN * DW_SPLIT_ALIGN
