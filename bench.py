@@ -699,6 +699,15 @@ def run_ours(args):
     # the step that is the part of the collective left exposed
     tail_ms = by_label.get("after_dw", 0.0)
     reduction_ms = by_label.get("dx_reduction")
+    # per-rank view: GPUs of one box differ by several percent under the power cap, and the
+    # one collective of the step makes every rank wait for the slowest
+    per_rank = None
+    if world > 1:
+        labels = names + ["dx_reduction", "after_dw"]
+        mine = torch.tensor([by_label.get(n, 0.0) for n in labels], device=dev, dtype=torch.float64)
+        allr = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        per_rank = {n: [round(float(t[i]), 4) for t in allr] for i, n in enumerate(labels)}
     if world > 1:
         tt = torch.tensor([total_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -960,6 +969,7 @@ def run_ours(args):
         "ms_x_sm_mhz": ms_per_step * sm_mhz if sm_mhz else None,
         "fwd_tokens_per_s": fwd_tokens_per_s,
         "gpu_launches": n_launches * world,
+        "per_rank_ms": per_rank,
         "clocks": clocks,
         "parity": parity,
         "roofline": roofline,
