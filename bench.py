@@ -28,7 +28,6 @@ import json
 import os
 import subprocess
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -128,50 +127,63 @@ REASON_BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal
                ("sw_power_cap", 0x4))
 
 
+# Runs in a child process (its own interpreter: polling must not compete with the
+# bench's launch loop for the GIL): NVML queries every 4 ms, one CSV line per sample.
+NVML_POLLER = r"""
+import sys, time
+import pynvml
+uuid, index, path = sys.argv[1], int(sys.argv[2]), sys.argv[3]
+pynvml.nvmlInit()
+try:
+    h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+except Exception:
+    h = pynvml.nvmlDeviceGetHandleByIndex(index)
+with open(path, "w", buffering=1) as f:
+    f.write("max,%d\n" % pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+    while True:
+        try:
+            f.write("%.6f,%d,%.3f,%d\n" % (time.time(), pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM),
+                                          pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0,
+                                          pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)))
+        except Exception:
+            pass
+        time.sleep(0.004)
+"""
+
+
 class ClockSampler:
     """Samples SM clock, power and clock-event reasons while a region runs: NVML
-    polled from a thread every few milliseconds (read-only queries, the ones
+    polled every few milliseconds by a child process (read-only queries, the ones
     nvidia-smi makes), or, if NVML cannot be loaded, an nvidia-smi loop."""
 
     def __init__(self, gpu_uuid: str, index: int):
         self.uuid, self.index = gpu_uuid, index
         self.rows = []  # (host time, sm MHz, power W, reasons bitmask)
         self.max_mhz = None
-        self._stop = threading.Event()
-        self._thread = None
+        self._nvml = None
+        self._nvml_path = None
         self._smi = None
         self._smi_path = None
         self.source = None
 
     def start(self):
-        try:
-            import pynvml
-
-            pynvml.nvmlInit()
-            try:
-                h = pynvml.nvmlDeviceGetHandleByUUID(self.uuid.encode() if isinstance(self.uuid, str) else self.uuid)
-            except Exception:
-                h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
-            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
-
-            def loop():
-                while not self._stop.is_set():
-                    try:
-                        self.rows.append((time.time(), float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)),
-                                          pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0,
-                                          int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))))
-                    except Exception:
-                        pass
-                    time.sleep(0.004)
-
-            self._thread = threading.Thread(target=loop, daemon=True)
-            self._thread.start()
-            self.source = "nvml, 4 ms period"
-            return
-        except Exception:
-            self._thread = None
         import tempfile
 
+        try:
+            import pynvml  # noqa: F401  (only to know that the child can import it)
+
+            fd, self._nvml_path = tempfile.mkstemp(prefix="fsw_clocks_", suffix=".csv")
+            os.close(fd)
+            self._nvml = subprocess.Popen([sys.executable, "-c", NVML_POLLER, self.uuid or "", str(self.index),
+                                           self._nvml_path], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+            time.sleep(0.5)
+            if self._nvml.poll() is None and os.path.getsize(self._nvml_path) > 0:
+                self.source = "nvml from a child process, 4 ms period"
+                return
+            self._nvml.kill()
+        except Exception:
+            pass
+        self._nvml = None
         fd, self._smi_path = tempfile.mkstemp(prefix="fsw_clocks_", suffix=".csv")
         os.close(fd)
         try:
@@ -184,10 +196,23 @@ class ClockSampler:
             self._smi = None
 
     def _finish(self):
-        if self._thread is not None:
-            self._stop.set()
-            self._thread.join(timeout=2)
-            self._thread = None
+        if self._nvml is not None:
+            self._nvml.terminate()
+            try:
+                self._nvml.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._nvml.kill()
+            self._nvml = None
+            for line in Path(self._nvml_path).read_text().splitlines():
+                f = line.split(",")
+                try:
+                    if f[0] == "max":
+                        self.max_mhz = float(f[1])
+                    elif len(f) == 4:
+                        self.rows.append((float(f[0]), float(f[1]), float(f[2]), int(f[3])))
+                except ValueError:
+                    continue
+            os.unlink(self._nvml_path)
         if self._smi is not None:
             import datetime
 
@@ -675,6 +700,7 @@ def run_ours(args):
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     launches["n"] = 0
+    kernels0 = _lib.get_option("kernel_launches")
     wall0 = time.time()
     t_start.record()
     step_marks = [[] for _ in range(K)]
@@ -683,7 +709,7 @@ def run_ours(args):
     t_end.record()
     barrier()
     wall1 = time.time()
-    n_launches = launches["n"]
+    n_launches = _lib.get_option("kernel_launches") - kernels0  # counted inside the library, second passes included
     clocks = None
     if rank == 0:
         clocks = sampler.summary(wall0, wall1, "timed region")

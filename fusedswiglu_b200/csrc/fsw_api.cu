@@ -10,6 +10,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "fsw_gemm.cuh"
@@ -60,6 +61,8 @@ struct Options {
   int64_t scatter_gap_ns = -1;    // pause between peer-store instructions of the dX scatter; -1 = from the tile's length
 };
 static Options g_opt;
+// Kernels this library has launched in this process (read through fsw_get_option("kernel_launches")).
+static std::atomic<long long> g_kernel_launches{0};
 
 // Status word the kernels write when a bounded wait gives up.
 __device__ uint32_t g_status_word;
@@ -337,6 +340,7 @@ static cudaError_t launch_one(const GemmParams& p, int grid, cudaStream_t st) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  ++g_kernel_launches;
   return cudaLaunchKernelEx(&cfg, gemm_kernel<MODE, CG, NSUB, T, ACC16>, p);
 }
 
@@ -545,6 +549,7 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
       const int rem = (int)(tiles - p.sk_first_tile);
       constexpr bool dual = (MODE == MODE_DW);
       const float4* w4 = reinterpret_cast<const float4*>(p.sk_ws);
+      ++g_kernel_launches;
       if (MODE == MODE_FWD && dtype == FSW_BF16)
         splitk_reduce_swiglu_kernel<__nv_bfloat16><<<rem * 16, 256, 0, st>>>(
             w4, p.store_gu ? p.c0_ptr : nullptr, p.c1_ptr, p.c2_ptr, p.M, p.N, p.num_m_tiles,
@@ -811,6 +816,7 @@ int64_t fsw_get_option(const char* name) {
       return -1;
     return v[1];
   }
+  if (!strcmp(name, "kernel_launches")) return (int64_t)g_kernel_launches.load();
   if (!strcmp(name, "map_cache_hits")) return (int64_t)g_map_hits;
   if (!strcmp(name, "map_cache_misses")) return (int64_t)g_map_misses;
   if (!strcmp(name, "last_sm_khz")) {
@@ -920,6 +926,7 @@ int fsw_backward_elementwise(const void* dout, const void* g, const void* u, voi
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ++g_kernel_launches;
   if (dtype == FSW_BF16)
     gate_grad_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(g),
@@ -949,6 +956,7 @@ int fsw_backward_elementwise_st(const void* dout, const void* s, const void* t, 
   const int64_t cap = (int64_t)d->sm_count * 32;
   if (blocks > cap) blocks = cap;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ++g_kernel_launches;
   if (dtype == FSW_BF16)
     gate_grad_st_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
         static_cast<const uint4*>(dout), static_cast<const uint4*>(s), static_cast<const uint4*>(t),
@@ -1106,6 +1114,7 @@ int fsw_dx_reduce(const void* recv, const void* own_slice, void* const* peer_fla
   if (blocks > cap) blocks = cap;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned long long limit = (unsigned long long)g_opt.wait_limit_ms * 1000000ull;
+  ++g_kernel_launches;
   if (dtype == FSW_BF16)
     dx_slices_reduce_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(
         static_cast<const uint4*>(recv), static_cast<const uint4*>(own_slice),
@@ -1125,6 +1134,7 @@ int fsw_wait_flags(void* flags, int n, uint32_t seq, void* stream) {
   DeviceInfo* d = nullptr;
   int rc = ensure_device(&d);
   if (rc != FSW_OK) return rc;
+  ++g_kernel_launches;
   wait_flags_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<unsigned int*>(flags), n, seq, d->status,
       (unsigned long long)g_opt.wait_limit_ms * 1000000ull);

@@ -278,7 +278,8 @@ int64_t fsw_status(void);
  * "l2_out" (L2 eviction priority of operand loads and forward stores: 0 normal,
  * 1 evict first, 2 evict last), "ew_blocks_per_sm".  Read-only facts through
  * fsw_get_option: "sm_count", "max_pairs", "stages", "last_sm_khz", "pace_off" (1 if
- * the last paced launch gave its pacing up), "map_cache_hits", "map_cache_misses".  Returns FSW_EINVAL for an unknown name
+ * the last paced launch gave its pacing up), "map_cache_hits", "map_cache_misses",
+ * "kernel_launches" (kernels launched by the library in this process so far).  Returns FSW_EINVAL for an unknown name
  * or value.  fsw_get_option returns the current value or -1.
  */
 int fsw_set_option(const char* name, int64_t value);
