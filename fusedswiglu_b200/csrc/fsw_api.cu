@@ -151,6 +151,9 @@ static int ensure_device(DeviceInfo** out) {
     FSW_CUDA((prepare_mode<MODE_DX, 2, 1>()));
     FSW_CUDA((prepare_mode<MODE_DW, 2, 1>()));
     FSW_CUDA((prepare_mode<MODE_FWD, 2, 2>()));
+    FSW_CUDA((prepare_mode<MODE_FWDST, 1, 1>()));
+    FSW_CUDA((prepare_mode<MODE_FWDST, 2, 1>()));
+    FSW_CUDA((prepare_mode<MODE_FWDST, 2, 2>()));
     FSW_CUDA((prepare_mode<MODE_DX, 2, 2>()));
     FSW_CUDA((prepare_mode<MODE_DW, 2, 2>()));
     FSW_CUDA((prepare_mode<MODE_DXG, 1, 1>()));
@@ -449,7 +452,7 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   const int cg = tc.cg;
   const int nsub = tc.nsub;
   const int tile_m = 128 * cg;
-  const int tile_n = ((MODE == MODE_FWD || MODE == MODE_DW) ? 128 : 256) * nsub;
+  const int tile_n = ((is_fwd(MODE) || MODE == MODE_DW) ? 128 : 256) * nsub;
   p.num_m_tiles = (rows + tile_m - 1) / tile_m;
   p.num_n_tiles = (p.N + tile_n - 1) / tile_n;
   if (p.ldc == 0) p.ldc = p.N;
@@ -550,11 +553,11 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
       constexpr bool dual = (MODE == MODE_DW);
       const float4* w4 = reinterpret_cast<const float4*>(p.sk_ws);
       ++g_kernel_launches;
-      if (MODE == MODE_FWD && dtype == FSW_BF16)
+      if (is_fwd(MODE) && dtype == FSW_BF16)
         splitk_reduce_swiglu_kernel<__nv_bfloat16><<<rem * 16, 256, 0, st>>>(
             w4, p.store_gu ? p.c0_ptr : nullptr, p.c1_ptr, p.c2_ptr, p.M, p.N, p.num_m_tiles,
             p.num_n_tiles, p.group_m, p.sk_first_tile, (int)ipt, p.sk_iters_per_cluster);
-      else if (MODE == MODE_FWD)
+      else if (is_fwd(MODE))
         splitk_reduce_swiglu_kernel<__half><<<rem * 16, 256, 0, st>>>(
             w4, p.store_gu ? p.c0_ptr : nullptr, p.c1_ptr, p.c2_ptr, p.M, p.N, p.num_m_tiles,
             p.num_n_tiles, p.group_m, p.sk_first_tile, (int)ipt, p.sk_iters_per_cluster);
@@ -899,10 +902,12 @@ static int forward_impl(const void* x, const void* w_gate, const void* w_up, voi
   p.N = (int)di;
   p.num_k_blocks = (int)((dm + 63) / 64);
   p.store_gu = g != nullptr;
-  p.save_st = save_st;
   p.c0_ptr = g;
   p.c1_ptr = u;
   p.c2_ptr = out;
+  if (save_st)
+    return run_gemm<MODE_FWDST>(p, (int)T, dtype, accum == FSW_ACC_F16, static_cast<cudaStream_t>(stream),
+                                d, choose_tiles(MODE_FWD, T, di, d));
   return run_gemm<MODE_FWD>(p, (int)T, dtype, accum == FSW_ACC_F16,
                             static_cast<cudaStream_t>(stream), d,
                             choose_tiles(MODE_FWD, T, di, d, 0, workspace != nullptr), 0, workspace,

@@ -51,7 +51,9 @@
 
 namespace fsw {
 
-enum : int { MODE_FWD = 0, MODE_DX = 1, MODE_DW = 2, MODE_NN = 3, MODE_NT = 4, MODE_TN = 5, MODE_DXG = 6 };
+enum : int { MODE_FWD = 0, MODE_DX = 1, MODE_DW = 2, MODE_NN = 3, MODE_NT = 4, MODE_TN = 5, MODE_DXG = 6, MODE_FWDST = 7 };
+// MODE_FWDST is MODE_FWD that saves s = silu(g) and t = u * silu'(g) where g and u would go.
+__host__ __device__ constexpr bool is_fwd(int mode) { return mode == MODE_FWD || mode == MODE_FWDST; }
 enum : int { MAJOR_K = 0, MAJOR_MN = 1 };
 
 // Codes written to the status word when a bounded wait gives up.
@@ -81,7 +83,6 @@ struct GemmParams {
   int num_m_tiles, num_n_tiles, group_m;
   int num_k_blocks;        // 64-wide K blocks per product
   int store_gu;            // MODE_FWD: also write g and u
-  int save_st;             // MODE_FWD: write s = silu(g) and t = u * silu'(g) in their place
   // MODE_DXG: dout, s, t (T x di, row-major, read with plain loads) and the dg / du
   // arrays that the tiles of column 0 write
   const void *gg_dout, *gg_s, *gg_t;
@@ -178,7 +179,7 @@ struct TileCfg {
   // the A operand is written by the epilogue warps instead of TMA
   static constexpr bool A_BY_WARPS = (MODE == MODE_DXG);
   // dual: the accumulator columns of a region are [128 from b0 | 128 from b1]
-  static constexpr bool DUAL_B = (MODE == MODE_FWD || MODE == MODE_DW);
+  static constexpr bool DUAL_B = (is_fwd(MODE) || MODE == MODE_DW);
   static constexpr int BM = 128;          // accumulator rows per CTA
   static constexpr int BN = 256;          // columns of one accumulator region (MMA N)
   static constexpr int BK = 64;           // one 128-byte swizzle row of 16-bit elements
@@ -513,7 +514,7 @@ __device__ __forceinline__ void load_pack16x2(uint32_t taddr_g, uint32_t taddr_u
 // 2 KB staging buffers.  A buffer is rewritten only after the bulk group that read it
 // has finished reading; phase B overlaps the next tile's MMAs, so these waits are
 // off the critical path.
-template <class C, typename T, bool ACC16, int NJB, class Release>
+template <class C, typename T, bool ACC16, int NJB, bool SAVE_ST, class Release>
 __device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& e, uint32_t taddr,
                                              int n0, int jb_begin, Release release) {
   const uint32_t buf0 = e.buf, buf1 = e.buf + 2048u;
@@ -531,24 +532,29 @@ __device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& 
     const uint32_t* pu = &U[c * 16];
     const int col = n0 + jb_begin * 64 + c * 32;
     const bool in_range = rows_ok && col < p.N;
-    // silu(g) rounded to the 16-bit type: a factor of out, and what is saved in place
-    // of g when the backward wants s = silu(g) and t = u * silu'(g) (save_st)
-    uint32_t ps[16], pt[16];
+    uint32_t po[16];
+    if (SAVE_ST) {
+      // s = silu(g), rounded: a factor of out, and what is saved in place of g
 #pragma unroll
-    for (int q = 0; q < 16; ++q) {
-      float g0, g1;
-      unpack2<T>(pg[q], g0, g1);
-      const float s0 = sigmoid_f32(g0), s1 = sigmoid_f32(g1);
-      const float silu0 = g0 * s0, silu1 = g1 * s1;
-      ps[q] = pack2<T>(silu0, silu1);
-      if (p.save_st)  // silu'(g) = sg + silu * (1 - sg), rounded, times u, rounded
-        pt[q] = mul2<T>(pu[q], pack2<T>(fmaf(silu0, 1.0f - s0, s0), fmaf(silu1, 1.0f - s1, s1)));
+      for (int q = 0; q < 16; ++q) {
+        float g0, g1;
+        unpack2<T>(pg[q], g0, g1);
+        po[q] = pack2<T>(g0 * sigmoid_f32(g0), g1 * sigmoid_f32(g1));
+      }
     }
     if (p.store_gu) {
       if (e.lane == 0) ptx::tma_store_wait_read<0>();
       __syncwarp();
-      if (p.save_st) {
-        stage_rows64(buf0, e.lane, ps);
+      if (SAVE_ST) {
+        stage_rows64(buf0, e.lane, po);
+        uint32_t pt[16];  // t = u * silu'(g); silu'(g) = sg + silu * (1 - sg), rounded, times u, rounded
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          float g0, g1;
+          unpack2<T>(pg[q], g0, g1);
+          const float s0 = sigmoid_f32(g0), s1 = sigmoid_f32(g1);
+          pt[q] = mul2<T>(pu[q], pack2<T>(fmaf(g0 * s0, 1.0f - s0, s0), fmaf(g1 * s1, 1.0f - s1, s1)));
+        }
         stage_rows64(buf1, e.lane, pt);
       } else {
         stage_rows64(buf0, e.lane, *reinterpret_cast<const uint32_t(*)[16]>(pg));
@@ -562,9 +568,16 @@ __device__ __forceinline__ void drain_swiglu(const GemmParams& p, const EpiCtx& 
         ptx::tma_store_commit();
       }
     }
-    uint32_t po[16];
 #pragma unroll
-    for (int q = 0; q < 16; ++q) po[q] = mul2<T>(ps[q], pu[q]);
+    for (int q = 0; q < 16; ++q) {
+      if (SAVE_ST) {
+        po[q] = mul2<T>(po[q], pu[q]);
+      } else {
+        float g0, g1;
+        unpack2<T>(pg[q], g0, g1);
+        po[q] = mul2<T>(pack2<T>(g0 * sigmoid_f32(g0), g1 * sigmoid_f32(g1)), pu[q]);
+      }
+    }
     if (e.lane == 0) ptx::tma_store_wait_read<0>();
     __syncwarp();
     stage_rows64(buf0, e.lane, po);
@@ -772,7 +785,7 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
     ptx::prefetch_tensormap(&p.b0);
     ptx::prefetch_tensormap(&p.b1);
     if (MODE == MODE_DX) ptx::prefetch_tensormap(&p.a1);
-    if (MODE == MODE_FWD) {
+    if (is_fwd(MODE)) {
       ptx::prefetch_tensormap(&p.sg);
       ptx::prefetch_tensormap(&p.su);
       ptx::prefetch_tensormap(&p.so);
@@ -1069,11 +1082,11 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
           release();
         } else if (NSUB == 2 && w.slot >= 0) {
           drain_partial<ACC16>(p, lane, taddr, w.slot, static_cast<int>(cta_rank), q, r, 0, 16, release);
-        } else if (MODE == MODE_FWD) {
+        } else if (is_fwd(MODE)) {
           if (split)
-            drain_swiglu<C, T, ACC16, 1>(p, e, taddr, rn0, chalf, release);
+            drain_swiglu<C, T, ACC16, 1, MODE == MODE_FWDST>(p, e, taddr, rn0, chalf, release);
           else
-            drain_swiglu<C, T, ACC16, 2>(p, e, taddr, rn0, 0, release);
+            drain_swiglu<C, T, ACC16, 2, MODE == MODE_FWDST>(p, e, taddr, rn0, 0, release);
         } else {
           if (split)
             drain_plain<C, MODE, T, ACC16, 2>(p, e, taddr, rn0, 2 * chalf, release);
@@ -1089,7 +1102,7 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
         if (a == 0) aph ^= 1u;
       }
     }
-    if (MODE == MODE_FWD) {
+    if (is_fwd(MODE)) {
       // all bulk stores of this warp must have completed before the CTA exits
       if (lane == 0) ptx::tma_store_wait_all<0>();
       __syncwarp();
