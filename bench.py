@@ -502,11 +502,12 @@ def run_ours(args):
         """The product backend with a labelled CUDA event recorded before each launch;
         the time from one event to the next is charged to the first one's label."""
         marks = None  # list of (label, event) of the step being timed, or None
+        pool = []     # events created before the timed region
 
         @staticmethod
         def mark(label):
             if Marked.marks is not None:
-                e = torch.cuda.Event(enable_timing=True)
+                e = Marked.pool.pop() if Marked.pool else torch.cuda.Event(enable_timing=True)
                 e.record()
                 Marked.marks.append((label, e))
 
@@ -700,10 +701,11 @@ def run_ours(args):
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     launches["n"] = 0
+    step_marks = [[] for _ in range(K)]
+    Marked.pool = [torch.cuda.Event(enable_timing=True) for _ in range(12 * K)]
     kernels0 = _lib.get_option("kernel_launches")
     wall0 = time.time()
     t_start.record()
-    step_marks = [[] for _ in range(K)]
     for i in range(K):
         step(step_marks[i])
     t_end.record()

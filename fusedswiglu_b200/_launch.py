@@ -37,12 +37,15 @@ def _stream(t: torch.Tensor) -> int:
 
 
 _WORKSPACE_BYTES = {}
+_WORKSPACES = {}
 
 
 def _workspace(t: torch.Tensor) -> Optional[torch.Tensor]:
     """Scratch for the split of a GEMM's last wave of tiles along K (see
-    fsw_workspace_bytes in the header).  Allocated per call from torch's caching
-    allocator, which keeps reuse stream-ordered; the library itself allocates nothing."""
+    fsw_workspace_bytes in the header): one buffer per (device, stream), allocated by
+    torch on first use and kept.  Launches on one stream run in order, so they can share
+    it; launches on different streams, which may overlap, get different buffers.  The
+    library itself allocates nothing."""
     dev = t.device.index
     if dev not in _WORKSPACE_BYTES:
         with torch.cuda.device(t.device):
@@ -50,7 +53,13 @@ def _workspace(t: torch.Tensor) -> Optional[torch.Tensor]:
         if n < 0:
             _lib.check("fsw_workspace_bytes", n)
         _WORKSPACE_BYTES[dev] = n
-    return torch.empty(_WORKSPACE_BYTES[dev], device=t.device, dtype=torch.uint8)
+    key = (dev, torch.cuda.current_stream(t.device).cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None  # no allocation inside a graph capture: the launch just does not split
+        ws = _WORKSPACES[key] = torch.empty(_WORKSPACE_BYTES[dev], device=t.device, dtype=torch.uint8)
+    return ws
 
 
 def forward(
