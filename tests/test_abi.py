@@ -197,3 +197,27 @@ def test_split_of_the_last_wave_covers_every_k_iteration_exactly_once():
                 have = [s for (m, n, it0, c, s) in sorted(order, key=lambda o: (o[0], o[1], o[2]))
                         if (m, n) == (m_.value, n_.value)]
                 assert have == want, (j, have, want)
+
+
+def test_argument_errors_of_the_multi_gpu_and_fused_entry_points():
+    lib = _lib.load()
+    P = ctypes.c_void_p
+    two = (P * 2)(P(16), P(32))
+    # world size outside 2..8, and T that does not split into rows that are multiples of 32
+    assert lib.fsw_backward_dx_scatter(P(16), P(16), P(16), P(16), two, 1, 0, 64, 64, 64, 0, 0, None) == -1
+    assert "world size" in _lib.last_error()
+    assert lib.fsw_backward_dx_scatter(P(16), P(16), P(16), P(16), two, 2, 0, 80, 64, 64, 0, 0, None) == -1
+    assert "multiple of 32" in _lib.last_error()
+    # reduction: rank outside the world, misaligned buffers
+    assert lib.fsw_dx_reduce(P(16), None, two, P(16), 2, 2, 1, 32, 64, P(16), 0, None) == -1
+    assert "rank" in _lib.last_error()
+    assert lib.fsw_dx_reduce(P(8), None, two, P(16), 2, 0, 1, 32, 64, P(16), 0, None) == -1
+    assert "aligned" in _lib.last_error()
+    assert lib.fsw_wait_flags(None, 2, 1, None) == -1
+    # fused gate gradient: every pointer is required, numel of the elementwise form a multiple of 8
+    assert lib.fsw_backward_dx_fused(P(16), None, P(16), P(16), P(16), P(16), P(16), P(16), 64, 64, 64, 0, None) == -1
+    assert "NULL" in _lib.last_error()
+    assert lib.fsw_backward_elementwise_st(P(16), P(16), P(16), P(16), P(16), 12, 0, None) == -1
+    assert lib.fsw_forward_st(P(16), P(16), P(16), P(16), None, None, 64, 64, 64, 0, 0, None) == -1
+    # workspace size must not be negative
+    assert lib.fsw_backward_dw_columns(P(16), P(16), P(16), P(16), P(16), 8, 64, 64, 0, 8, 0, None, -1, 0, 0, None) == -1

@@ -1,5 +1,7 @@
-"""Column-parallel mode on real GPUs: two NCCL ranks, one per GPU, against the
-unsharded single-GPU result.  Skipped on a box with fewer than two GPUs."""
+"""Column-parallel mode on real GPUs.  Two ranks, one per GPU, against the unsharded
+single-GPU result (NCCL and the library's own peer-memory reduction; skipped on a box
+with fewer than two GPUs), and the kernels of the peer-memory reduction with the ranks
+emulated on one GPU."""
 import os
 import socket
 import sys
@@ -161,3 +163,82 @@ def test_two_gpu_column_parallel_matches_single_gpu():
         # tensor-parallel MLP: partial sums are rounded per rank before the all-reduce
         for k, v in r["mlp"].items():
             assert v < 1e-2, (rank, k, r["mlp"])
+
+
+def test_dx_scatter_and_reduction_with_the_ranks_emulated_on_one_gpu():
+    """The kernels of the peer-memory dX reduction on ONE GPU: four 'ranks' with their own
+    operands take turns on the device, every rank's receive buffer is local memory.  The
+    scattering GEMM must put each rank's partial rows exactly where the owner expects
+    them (tile order rotated per rank), and the reduction must give the fp32 sum of the
+    slices in rank order, rounded once.  The flags are set from the host beforehand, so no
+    kernel waits for another one."""
+    import ctypes
+
+    from fusedswiglu_b200 import _launch, _lib
+
+    world, T, dm, di = 4, 2048, 512, 1024
+    rows = T // world
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    mk = lambda *s: torch.randn(*s, device="cuda", dtype=torch.bfloat16, generator=gen)
+    ops = [(mk(T, di), mk(T, di), mk(dm, di) / di ** 0.5, mk(dm, di) / di ** 0.5) for _ in range(world)]
+    recv = [torch.full((world, rows, dm), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    ptrs = [r.data_ptr() for r in recv]
+    partial = []
+    for r, (dg, du, wg, wu) in enumerate(ops):
+        _launch.grad_input_scatter(dg, du, wg, wu, ptrs, world, r)
+        partial.append(_launch.grad_input(dg, du, wg, wu, split_k=False))
+    torch.cuda.synchronize()
+    for owner in range(world):
+        for src in range(world):
+            assert torch.equal(recv[owner][src], partial[src][owner * rows:(owner + 1) * rows]), (owner, src)
+    seq = 7
+    flags = [torch.full((world,), seq, device="cuda", dtype=torch.int32) for _ in range(world)]
+    fptrs = [f.data_ptr() for f in flags]
+    for r in range(world):
+        want = torch.zeros(rows, dm, device="cuda", dtype=torch.float32)
+        for s in range(world):
+            want += partial[s][r * rows:(r + 1) * rows].float()
+        out = torch.full((rows, dm), float("nan"), device="cuda", dtype=torch.bfloat16)
+        _launch.reduce_dx_slices(ptrs[r], fptrs, fptrs[r], world, r, seq, out)
+        # the own slice read in place instead of from the receive buffer
+        out2 = torch.empty_like(out)
+        recv[r][r].fill_(float("nan"))
+        _launch.reduce_dx_slices(ptrs[r], fptrs, fptrs[r], world, r, seq, out2,
+                                 own_slice=partial[r][r * rows:(r + 1) * rows])
+        torch.cuda.synchronize()
+        assert torch.equal(out, want.to(torch.bfloat16)) and torch.equal(out2, out), r
+    assert _lib.device_status() == 0
+
+
+def test_a_reduction_whose_peers_never_signal_gives_up_and_reports_it():
+    """No peer ever writes the flags: the reduction's time-limited wait runs out, the kernel
+    records a status code, writes nothing and returns; the context stays usable.  (The wait
+    is made to run out by a flag that nothing sets - no fault, no trap, no endless loop.)"""
+    from fusedswiglu_b200 import _launch, _lib
+
+    world, rows, dm = 2, 64, 64
+    recv = torch.ones(world, rows, dm, device="cuda", dtype=torch.bfloat16)
+    flags = torch.zeros(world, device="cuda", dtype=torch.int32)  # stay 0; the step number is 1
+    out = torch.full((rows, dm), 5.0, device="cuda", dtype=torch.bfloat16)
+    assert _lib.device_status() == 0
+    old = _lib.get_option("wait_limit_ms")
+    _lib.set_option("wait_limit_ms", 50)
+    try:
+        # this rank's own signal goes to word [1] of a scratch array, so word [1] of `flags` stays 0 too
+        scratch = torch.zeros(world, device="cuda", dtype=torch.int32)
+        _launch.reduce_dx_slices(recv.data_ptr(), [scratch.data_ptr(), scratch.data_ptr()], flags.data_ptr(),
+                                 world, 1, 1, out)
+        _launch.wait_flags(flags.data_ptr(), world, 1, out)
+        torch.cuda.synchronize()
+        status = _lib.load().fsw_status()
+    finally:
+        _lib.set_option("wait_limit_ms", old)
+    assert status != 0 and (status & 0x7F) == 5, status       # WAIT_PEER_PARTIALS
+    assert "bounded wait" in _lib.last_error()
+    assert bool((out == 5.0).all())                           # nothing was written
+    assert _lib.device_status() == 0                          # reading the status cleared it
+    flags.fill_(1)
+    _launch.reduce_dx_slices(recv.data_ptr(), [scratch.data_ptr(), scratch.data_ptr()], flags.data_ptr(),
+                             world, 1, 1, out)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0 and bool((out == 2.0).all())
