@@ -1,7 +1,11 @@
 // C ABI of libfused_swiglu_sm100.so (declared in include/fused_swiglu.h):
 // argument checking, TMA tensor-map construction, UMMA descriptor constants and
-// kernel launches.  No device memory is allocated here; the only per-device
-// state is a cache of device attributes.
+// kernel launches.  No device memory is allocated here: scratch (dg/du, the
+// workspace of a split last wave, multi-GPU receive buffers) is the caller's.  State
+// kept by the library: process-wide options, a cache of device attributes and of
+// encoded tensor maps, and per device a status word, a clock probe, a ring of pacing
+// counters and the fixed scratch of fsw_backward_static_scratch (all `__device__`
+// variables of the library image).
 #include "../../include/fused_swiglu.h"
 
 #include <cuda.h>
