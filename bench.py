@@ -445,8 +445,9 @@ def run_ours(args):
 
     # The dX collective runs on a group whose NCCL kernels are capped to as many CTAs
     # as the dW GEMM leaves SMs free for them.
-    group = parallel.new_collective_group(max_ctas=args.comm_ctas) if world > 1 and args.comm_ctas > 0 else None
     use_peer = world > 1 and args.dx_collective in ("peer", "peer-copy")
+    group = (parallel.new_collective_group(max_ctas=args.comm_ctas)
+             if world > 1 and args.comm_ctas > 0 and not use_peer else None)
 
     _lib.load()
     for item in args.opt:
@@ -551,8 +552,21 @@ def run_ours(args):
 
     reducer = None
     if use_peer:
-        real_reducer = parallel.PeerDxReducer(T, dm, tdt, dev, group,
-                                              scatter="copy" if args.dx_collective == "peer-copy" else "epilogue")
+        # Symmetric memory needs peer access between all GPUs of the job; if it cannot be set
+        # up on every rank, all ranks fall back to NCCL together.
+        try:
+            real_reducer = parallel.PeerDxReducer(T, dm, tdt, dev, group,
+                                                  scatter="copy" if args.dx_collective == "peer-copy" else "epilogue")
+            ok = torch.ones(1, device=dev)
+        except Exception as exc:  # noqa: BLE001
+            real_reducer, ok = None, torch.zeros(1, device=dev)
+            print(f"rank {rank}: peer-memory reduction unavailable ({type(exc).__name__}: {exc}); using NCCL",
+                  file=sys.stderr, flush=True)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok.item()) == 0.0:
+            real_reducer, use_peer = None, False
+            group = parallel.new_collective_group(max_ctas=args.comm_ctas) if args.comm_ctas > 0 else None
+    if use_peer:
 
         class MarkedReducer:
             """The product's reducer with the same labelled events."""
