@@ -221,6 +221,25 @@ def grad_input_fused(dout: torch.Tensor, s: torch.Tensor, t: torch.Tensor, w_gat
     return dx, dg, du
 
 
+def gate_grad_and_input(dout: torch.Tensor, g: torch.Tensor, u: torch.Tensor, w_gate: torch.Tensor,
+                        w_up: torch.Tensor, *, split_k: bool = True) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(dX, dg, du) in one launch: the gate-gradient step runs inside the dX GEMM kernel, on
+    its otherwise idle epilogue warps (bit-identical to gate_grad + grad_input)."""
+    _require_cuda(dout, g, u, w_gate, w_up)
+    T, di = dout.shape
+    dm = w_gate.shape[0]
+    dx = torch.empty((T, dm), device=dout.device, dtype=dout.dtype)
+    dg, du = torch.empty_like(dout), torch.empty_like(dout)
+    ws = _workspace(dout) if split_k and T > 0 else None
+    with torch.cuda.device(dout.device):
+        rc = _lib.load().fsw_backward_dx_gate(
+            dout.data_ptr(), g.data_ptr(), u.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), dx.data_ptr(),
+            dg.data_ptr(), du.data_ptr(), T, dm, di, ws.data_ptr() if ws is not None else None,
+            ws.numel() if ws is not None else 0, _code(dout), _stream(dout))
+    _lib.check("fsw_backward_dx_gate", rc)
+    return dx, dg, du
+
+
 def gate_grad_from_factors(dout: torch.Tensor, s: torch.Tensor, t: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """(dg, du) = (dout * t, dout * s) as a kernel of its own."""
     _require_cuda(dout, s, t)

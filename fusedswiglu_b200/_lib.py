@@ -29,6 +29,7 @@ SIGNATURES = {
     "fsw_forward_st": (c_int, [c_void_p] * 6 + [c_int64] * 3 + [c_int, c_int, c_void_p]),
     "fsw_backward_dx_fused": (c_int, [c_void_p] * 8 + [c_int64] * 3 + [c_int, c_void_p]),
     "fsw_backward_elementwise_st": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_void_p]),
+    "fsw_backward_dx_gate": (c_int, [c_void_p] * 8 + [c_int64] * 3 + [c_void_p, c_int64, c_int, c_void_p]),
     "fsw_backward_dx_ws": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_void_p, c_int64, c_int, c_int, c_void_p]),
     "fsw_workspace_bytes": (c_int64, []),
     "fsw_backward": (c_int, [c_void_p] * 11 + [c_int64] * 3 + [c_int, c_int, c_void_p]),

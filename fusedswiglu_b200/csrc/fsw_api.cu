@@ -62,6 +62,8 @@ struct Options {
   int64_t pace_limit_us = 50;    // longest wait at one meeting point
   int64_t ew_blocks_per_sm = 32;  // grid cap of the elementwise kernel, per SM
   int64_t split_k = 1;            // 0: never split the last wave of tiles along K
+  int64_t ew_ahead = 0;           // row tiles the gate-gradient side job may run ahead (0 = one wave + 2)
+  int64_t gate_in_dx = 1;         // 0: fsw_backward_dx_gate runs the elementwise step as a launch of its own
   int64_t scatter_gap_ns = -1;    // pause between peer-store instructions of the dX scatter; -1 = from the tile's length
 };
 static Options g_opt;
@@ -75,6 +77,11 @@ __device__ uint32_t g_status_word;
 // (other streams, other host threads) do not disturb each other's counts.
 constexpr int kPaceSlots = 16;
 __device__ unsigned int g_pace[2 * kPaceSlots];
+// Ticket and per-row-tile counters of the gate-gradient side job of MODE_DXE launches;
+// a ring of slots, one per launch in turn (see g_pace).
+constexpr int kEwSlots = 4;
+constexpr int kEwMaxRowTiles = 8192;
+__device__ unsigned int g_ew_ctrl[kEwSlots * (2 + kEwMaxRowTiles)];
 // SM cycles and nanoseconds that CTA 0 of the last GEMM launch was resident.
 __device__ unsigned long long g_clk_probe[8];
 
@@ -88,6 +95,8 @@ struct DeviceInfo {
   uint32_t* status = nullptr;
   unsigned long long* clk_probe = nullptr;
   unsigned int* pace = nullptr;
+  unsigned int* ew_ctrl = nullptr;
+  unsigned int ew_next = 0;     // next slot of g_ew_ctrl to hand out
   unsigned int pace_next = 0;   // next slot of g_pace to hand out
   unsigned int pace_last = 0;   // slot the last paced launch used
 };
@@ -160,6 +169,9 @@ static int ensure_device(DeviceInfo** out) {
     FSW_CUDA((prepare_mode<MODE_FWDST, 2, 2>()));
     FSW_CUDA((prepare_mode<MODE_DX, 2, 2>()));
     FSW_CUDA((prepare_mode<MODE_DW, 2, 2>()));
+    FSW_CUDA((prepare_mode<MODE_DXE, 1, 1>()));
+    FSW_CUDA((prepare_mode<MODE_DXE, 2, 1>()));
+    FSW_CUDA((prepare_mode<MODE_DXE, 2, 2>()));
     FSW_CUDA((prepare_mode<MODE_DXG, 1, 1>()));
     FSW_CUDA((prepare_mode<MODE_DXG, 2, 1>()));
     FSW_CUDA((prepare_mode<MODE_DXG, 2, 2>()));
@@ -179,6 +191,8 @@ static int ensure_device(DeviceInfo** out) {
     d.clk_probe = static_cast<unsigned long long*>(sp);
     FSW_CUDA(cudaGetSymbolAddress(&sp, g_pace));
     d.pace = static_cast<unsigned int*>(sp);
+    FSW_CUDA(cudaGetSymbolAddress(&sp, g_ew_ctrl));
+    d.ew_ctrl = static_cast<unsigned int*>(sp);
     // How many CTA pairs can be resident at once (a GPC with an odd SM count
     // leaves one SM without a partner).
     {
@@ -468,7 +482,7 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
   p.wait_limit_ns = (unsigned long long)g_opt.wait_limit_ms * 1000000ull;
   p.stall_producer = (int)g_opt.stall_producer;
   const int a_major = (MODE == MODE_DW || MODE == MODE_TN) ? MAJOR_MN : MAJOR_K;
-  const int b_major = (MODE == MODE_DX || MODE == MODE_NT || MODE == MODE_DXG) ? MAJOR_K : MAJOR_MN;
+  const int b_major = (is_dx(MODE) || MODE == MODE_NT || MODE == MODE_DXG) ? MAJOR_K : MAJOR_MN;
   fill_operand_desc(a_major, &p.a_desc, &p.a_kadv);
   fill_operand_desc(b_major, &p.b_desc, &p.b_kadv);
   p.idesc = make_idesc(dtype, acc16, a_major, b_major, 128 * cg, 256);
@@ -538,7 +552,7 @@ static int run_gemm(GemmParams& p, int rows, int dtype, bool acc16, cudaStream_t
     int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
     // Split the last partial wave along K over all pairs when the caller gave a
     // workspace and the tail would otherwise idle most of the GPU.
-    constexpr int nseg = (MODE == MODE_DX || MODE == MODE_DXG) ? 2 : 1;
+    constexpr int nseg = (is_dx(MODE) || MODE == MODE_DXG) ? 2 : 1;
     const long long ipt = (long long)nseg * p.num_k_blocks;
     p.sk_total_iters = 0;
     if (nsub == 2 && ws != nullptr && g_opt.split_k != 0 &&
@@ -606,38 +620,6 @@ __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
 template <>
 __device__ __forceinline__ float to_f32<__half>(__half v) {
   return __half2float(v);
-}
-
-// 16-byte streaming load / store: every operand is touched once per launch.
-__device__ __forceinline__ uint4 ld_stream(const void* p) {
-  uint4 v;
-  asm("ld.global.nc.L1::no_allocate.v4.b32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
-// One 16-byte vector (8 elements).  Only g is widened to fp32 (sigmoid); the
-// products are packed 16-bit multiplies, each rounding once like the fp32 form.
-template <typename T>
-__device__ __forceinline__ void gate_grad_vec(const uint4& vd, const uint4& vg, const uint4& vu,
-                                              uint4& odg, uint4& odu) {
-  const uint32_t* wd = reinterpret_cast<const uint32_t*>(&vd);
-  const uint32_t* wg = reinterpret_cast<const uint32_t*>(&vg);
-  const uint32_t* wu = reinterpret_cast<const uint32_t*>(&vu);
-  uint32_t* wdg = reinterpret_cast<uint32_t*>(&odg);
-  uint32_t* wdu = reinterpret_cast<uint32_t*>(&odu);
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    float g0, g1;
-    unpack2<T>(wg[e], g0, g1);
-    const float s0 = sigmoid_f32(g0), s1 = sigmoid_f32(g1);
-    const float silu0 = g0 * s0, silu1 = g1 * s1;
-    const uint32_t silu = pack2<T>(silu0, silu1);
-    const uint32_t dsilu = pack2<T>(fmaf(silu0, 1.0f - s0, s0), fmaf(silu1, 1.0f - s1, s1));
-    wdu[e] = mul2<T>(wd[e], silu);
-    wdg[e] = mul2<T>(mul2<T>(wd[e], wu[e]), dsilu);
-  }
 }
 
 constexpr int kGateGradUnroll = 4;  // 16-byte vectors per thread and tensor in flight
@@ -784,6 +766,12 @@ int fsw_set_option(const char* name, int64_t value) {
   } else if (!strcmp(name, "split_k")) {
     if (value != 0 && value != 1) return fail(FSW_EINVAL, "split_k must be 0 or 1");
     g_opt.split_k = value;
+  } else if (!strcmp(name, "ew_ahead")) {
+    if (value < 0 || value > 100000) return fail(FSW_EINVAL, "ew_ahead must be in [0, 100000]");
+    g_opt.ew_ahead = value;
+  } else if (!strcmp(name, "gate_in_dx")) {
+    if (value != 0 && value != 1) return fail(FSW_EINVAL, "gate_in_dx must be 0 or 1");
+    g_opt.gate_in_dx = value;
   } else if (!strcmp(name, "scatter_gap_ns")) {
     if (value < -1 || value > 100000) return fail(FSW_EINVAL, "scatter_gap_ns must be in [-1, 100000]");
     g_opt.scatter_gap_ns = value;
@@ -804,6 +792,8 @@ int64_t fsw_get_option(const char* name) {
   if (!strcmp(name, "ew_blocks_per_sm")) return g_opt.ew_blocks_per_sm;
   if (!strcmp(name, "split_k")) return g_opt.split_k;
   if (!strcmp(name, "scatter_gap_ns")) return g_opt.scatter_gap_ns;
+  if (!strcmp(name, "gate_in_dx")) return g_opt.gate_in_dx;
+  if (!strcmp(name, "ew_ahead")) return g_opt.ew_ahead;
   if (!strcmp(name, "gemm_max_sms")) return g_opt.gemm_max_sms;
   if (!strcmp(name, "wait_limit_ms")) return g_opt.wait_limit_ms;
   if (!strcmp(name, "stall_producer")) return g_opt.stall_producer;
@@ -1010,6 +1000,63 @@ int fsw_backward_dx_fused(const void* dout, const void* s, const void* t, const 
   p.gg_du = du;
   p.gg_k = (int)di;
   return run_gemm<MODE_DXG>(p, (int)T, dtype, false, static_cast<cudaStream_t>(stream), d, tc);
+}
+
+// Gate-gradient step and dX in one launch: the elementwise work is done once, by the
+// GEMM kernel's own epilogue warps while they wait for accumulators, ahead of the tiles
+// that read dg and du.  Results are those of fsw_backward_elementwise + fsw_backward_dx_ws.
+int fsw_backward_dx_gate(const void* dout, const void* g, const void* u, const void* w_gate,
+                         const void* w_up, void* dx, void* dg, void* du, int64_t T, int64_t dm,
+                         int64_t di, void* workspace, int64_t workspace_bytes, int dtype, void* stream) {
+  int rc = check_common(T, dm, di, dtype, FSW_ACC_F32);
+  if (rc != FSW_OK) return rc;
+  if (T == 0) return FSW_OK;
+  if (!dout || !g || !u || !w_gate || !w_up || !dx || !dg || !du) return fail(FSW_EINVAL, "NULL pointer");
+  if (!aligned16(dout) || !aligned16(g) || !aligned16(u) || !aligned16(w_gate) || !aligned16(w_up) ||
+      !aligned16(dx) || !aligned16(dg) || !aligned16(du))
+    return fail(FSW_EINVAL, "pointers must be 16-byte aligned");
+  DeviceInfo* d = nullptr;
+  if ((rc = ensure_device(&d)) != FSW_OK) return rc;
+  const TileChoice tc = choose_tiles(MODE_DX, T, dm, d, 0, workspace != nullptr);
+  const int64_t row_tiles = (T + 255) / 256;
+  if (tc.cg != 2 || row_tiles > kEwMaxRowTiles || g_opt.gate_in_dx == 0) {
+    // the side job is written for 256-row tiles of CTA pairs: otherwise two launches
+    if ((rc = fsw_backward_elementwise(dout, g, u, dg, du, T * di, dtype, stream)) != FSW_OK) return rc;
+    return fsw_backward_dx_ws(dg, du, w_gate, w_up, dx, T, dm, di, workspace, workspace_bytes, dtype,
+                              FSW_ACC_F32, stream);
+  }
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  if ((rc = make_map(&p.a0, dg, dtype, di, T, 128, "dg")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.a1, du, dtype, di, T, 128, "du")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.b0, w_gate, dtype, di, dm, 256 / tc.cg, "w_gate")) != FSW_OK) return rc;
+  if ((rc = make_map(&p.b1, w_up, dtype, di, dm, 256 / tc.cg, "w_up")) != FSW_OK) return rc;
+  p.c0_ptr = dx;
+  p.M = (int)T;
+  p.N = (int)dm;
+  p.num_k_blocks = (int)((di + 63) / 64);
+  p.ew_dout = dout;
+  p.ew_g = g;
+  p.ew_u = u;
+  p.ew_dg = dg;
+  p.ew_du = du;
+  p.ew_cols = (int)di;
+  p.ew_qpm = (int)(256 * di / 2048);
+  {
+    // one wave of tiles ahead: the row tiles that a wave of SM pairs works on at once, plus two
+    const int64_t n_tiles = (dm + 511) / 512;
+    const int64_t ahead = g_opt.ew_ahead > 0 ? g_opt.ew_ahead : (d->max_pairs + n_tiles - 1) / n_tiles + 2;
+    p.ew_ahead = (int)(ahead < 1 ? 1 : ahead);
+  }
+  unsigned int slot;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    slot = d->ew_next++ % kEwSlots;
+  }
+  p.ew_ctrl = d->ew_ctrl + (size_t)slot * (2 + kEwMaxRowTiles);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  FSW_CUDA(cudaMemsetAsync(p.ew_ctrl, 0, (size_t)(2 + row_tiles) * sizeof(unsigned int), st));
+  return run_gemm<MODE_DXE>(p, (int)T, dtype, false, st, d, tc, 0, workspace, workspace_bytes);
 }
 
 int fsw_backward_dx(const void* dg, const void* du, const void* w_gate, const void* w_up, void* dx,

@@ -51,9 +51,13 @@
 
 namespace fsw {
 
-enum : int { MODE_FWD = 0, MODE_DX = 1, MODE_DW = 2, MODE_NN = 3, MODE_NT = 4, MODE_TN = 5, MODE_DXG = 6, MODE_FWDST = 7 };
+enum : int { MODE_FWD = 0, MODE_DX = 1, MODE_DW = 2, MODE_NN = 3, MODE_NT = 4, MODE_TN = 5, MODE_DXG = 6, MODE_FWDST = 7, MODE_DXE = 8 };
 // MODE_FWDST is MODE_FWD that saves s = silu(g) and t = u * silu'(g) where g and u would go.
 __host__ __device__ constexpr bool is_fwd(int mode) { return mode == MODE_FWD || mode == MODE_FWDST; }
+// MODE_DXE is MODE_DX whose otherwise idle epilogue warps also do the gate-gradient
+// elementwise step (dg, du from dout, g, u), once per element, ahead of the tiles that
+// read dg and du through TMA; see GemmParams::ew_*.
+__host__ __device__ constexpr bool is_dx(int mode) { return mode == MODE_DX || mode == MODE_DXE; }
 enum : int { MAJOR_K = 0, MAJOR_MN = 1 };
 
 // Codes written to the status word when a bounded wait gives up.
@@ -65,6 +69,7 @@ enum : uint32_t {
   WAIT_EPI_TMEM_FULL = 4,
   WAIT_XFORM_EMPTY = 6,   // (5 is WAIT_PEER_PARTIALS, below)
   WAIT_MMA_XFORM = 7,
+  WAIT_GATE_GRAD_ROWS = 8,
 };
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // default limit per wait: 2 s
@@ -88,6 +93,22 @@ struct GemmParams {
   const void *gg_dout, *gg_s, *gg_t;
   void *gg_dg, *gg_du;
   int gg_k;                // di: row length of the five arrays above
+  // MODE_DXE: the elementwise step as a side job of the epilogue warps.  The (T, di)
+  // arrays are cut, in the order the row tiles are visited, into quanta of 2048
+  // elements (256 * di is a multiple of 2048, so no quantum straddles two row tiles):
+  // row tile number v in visiting order owns quanta [v * ew_qpm, (v + 1) * ew_qpm).  Idle
+  // epilogue warps of all CTAs take quanta from ew_ctrl[0] (an atomic ticket), compute
+  // dg and du, and add 1 to ew_ctrl[2 + v]; a tile's TMA producer waits - time-limited -
+  // until its row tile's count has reached ew_qpm before it loads dg / du tiles.  The
+  // side job stays at most ew_ahead row tiles ahead of the furthest row tile any producer
+  // has asked for (ew_ctrl[1] - 1): done all at once it would stream through L2 at HBM
+  // speed and evict the operand panels the tiles share.
+  const void *ew_dout, *ew_g, *ew_u;
+  void *ew_dg, *ew_du;
+  unsigned int* ew_ctrl;
+  int ew_qpm;              // quanta per row tile = 256 * di / 2048
+  int ew_ahead;            // row tiles the side job may run ahead
+  int ew_cols;             // di
   int l2_a, l2_b;          // L2 eviction priority of A / B loads: 0 normal, 1 first, 2 last
   int l2_out;              // same for the forward's output stores
   uint32_t* status;        // device status word (0 = ok)
@@ -175,7 +196,7 @@ template <int MODE, int CG, int NSUB>
 struct TileCfg {
   static_assert(NSUB == 1 || (NSUB == 2 && CG == 2), "512-column tiles need a CTA pair");
   static constexpr int A_MAJOR = (MODE == MODE_DW || MODE == MODE_TN) ? MAJOR_MN : MAJOR_K;
-  static constexpr int B_MAJOR = (MODE == MODE_DX || MODE == MODE_NT || MODE == MODE_DXG) ? MAJOR_K : MAJOR_MN;
+  static constexpr int B_MAJOR = (is_dx(MODE) || MODE == MODE_NT || MODE == MODE_DXG) ? MAJOR_K : MAJOR_MN;
   // the A operand is written by the epilogue warps instead of TMA
   static constexpr bool A_BY_WARPS = (MODE == MODE_DXG);
   // dual: the accumulator columns of a region are [128 from b0 | 128 from b1]
@@ -200,7 +221,7 @@ struct TileCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int NSEG = (MODE == MODE_DX || MODE == MODE_DXG) ? 2 : 1;
+  static constexpr int NSEG = (is_dx(MODE) || MODE == MODE_DXG) ? 2 : 1;
   // Output columns covered by one accumulator region / one tile, per output tensor.
   static constexpr int REGION_N = DUAL_B ? 128 : 256;
   static constexpr int TILE_N = REGION_N * NSUB;
@@ -616,7 +637,7 @@ __device__ __forceinline__ void drain_plain(const GemmParams& p, const EpiCtx& e
   }
   void* scatter_out = nullptr;
   unsigned int gap_ns = 0;
-  if (MODE == MODE_DX && p.scatter_world > 1) {
+  if (is_dx(MODE) && p.scatter_world > 1) {
     // The warp's 32 rows have one owner (scatter_rows is a multiple of 32).  Row t of
     // dX is row (rank * scatter_rows + t - owner * scatter_rows) of the owner's buffer.
     int owner = e.row0 / p.scatter_rows;
@@ -630,7 +651,7 @@ __device__ __forceinline__ void drain_plain(const GemmParams& p, const EpiCtx& e
     const int jb = jb_begin + j;
     const int col = (MODE == MODE_DW) ? (n0 + (jb & 1) * 64) : (n0 + jb * 64);
     void* out = (MODE == MODE_DW && jb >= 2) ? p.c1_ptr : p.c0_ptr;
-    if (MODE == MODE_DX && p.scatter_world > 1) out = scatter_out;
+    if (is_dx(MODE) && p.scatter_world > 1) out = scatter_out;
     if (FSW_PLAIN_ONE_PHASE) {  // measurement build: read, release after the last read, store box by box
       read_box(j);
       if (j == NJB - 1) release();
@@ -674,6 +695,39 @@ __device__ __forceinline__ void drain_partial(const GemmParams& p, int lane, uin
       }
       ptx::st_global_v4(ws + splitk_vec_index(slot, cta, q, r, c, j, lane), w[0], w[1], w[2], w[3]);
     }
+  }
+}
+
+// ---------------------------------------------- gate-gradient arithmetic --
+// 16-byte streaming load / store: every operand is touched once per launch.
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm("ld.global.nc.L1::no_allocate.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// One 16-byte vector (8 elements).  Only g is widened to fp32 (sigmoid); the
+// products are packed 16-bit multiplies, each rounding once like the fp32 form.
+template <typename T>
+__device__ __forceinline__ void gate_grad_vec(const uint4& vd, const uint4& vg, const uint4& vu,
+                                              uint4& odg, uint4& odu) {
+  const uint32_t* wd = reinterpret_cast<const uint32_t*>(&vd);
+  const uint32_t* wg = reinterpret_cast<const uint32_t*>(&vg);
+  const uint32_t* wu = reinterpret_cast<const uint32_t*>(&vu);
+  uint32_t* wdg = reinterpret_cast<uint32_t*>(&odg);
+  uint32_t* wdu = reinterpret_cast<uint32_t*>(&odu);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float g0, g1;
+    unpack2<T>(wg[e], g0, g1);
+    const float s0 = sigmoid_f32(g0), s1 = sigmoid_f32(g1);
+    const float silu0 = g0 * s0, silu1 = g1 * s1;
+    const uint32_t silu = pack2<T>(silu0, silu1);
+    const uint32_t dsilu = pack2<T>(fmaf(silu0, 1.0f - s0, s0), fmaf(silu1, 1.0f - s1, s1));
+    wdu[e] = mul2<T>(wd[e], silu);
+    wdg[e] = mul2<T>(mul2<T>(wd[e], wu[e]), dsilu);
   }
 }
 
@@ -730,6 +784,55 @@ __device__ __forceinline__ void gate_grad_write(const GemmParams& p, int tid, in
   }
 }
 
+// One quantum of the MODE_DXE side job, by a whole warp: 2048 elements = 256 vectors of
+// 8; lane l takes vectors l, l + 32, ... (8 of them, in two rounds of 4 so that 12 loads
+// are in flight per lane).  Quantum `q` belongs to row tile (q / ew_qpm + m_rotate) mod
+// num_m_tiles, the order in which the tiles visit the rows; a quantum beyond the end of the
+// arrays (ragged last row tile) is empty.  Finishing a quantum - after a fence, so that
+// the results are visible GPU-wide first - adds 1 to the row tile's count.
+template <typename T, int TILE_M>
+__device__ __forceinline__ void gate_grad_quantum(const GemmParams& p, unsigned int q, int lane) {
+  const unsigned int v = q / static_cast<unsigned int>(p.ew_qpm);
+  const unsigned int j = q - v * static_cast<unsigned int>(p.ew_qpm);
+  int m = static_cast<int>(v) + p.m_rotate;
+  if (m >= p.num_m_tiles) m -= p.num_m_tiles;
+  const long long total_vec = static_cast<long long>(p.M) * p.ew_cols / 8;
+  const long long first = (static_cast<long long>(m) * TILE_M * p.ew_cols) / 8 + static_cast<long long>(j) * 256;
+  const uint4* d4 = static_cast<const uint4*>(p.ew_dout);
+  const uint4* g4 = static_cast<const uint4*>(p.ew_g);
+  const uint4* u4 = static_cast<const uint4*>(p.ew_u);
+  uint4* dg4 = static_cast<uint4*>(p.ew_dg);
+  uint4* du4 = static_cast<uint4*>(p.ew_du);
+#pragma unroll 1
+  for (int round = 0; round < 2; ++round) {
+    uint4 vd[4], vg[4], vu[4];
+    bool in[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const long long idx = first + (round * 4 + i) * 32 + lane;
+      in[i] = idx < total_vec;
+      if (in[i]) {
+        vd[i] = ld_stream(d4 + idx);
+        vg[i] = ld_stream(g4 + idx);
+        vu[i] = ld_stream(u4 + idx);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (in[i]) {
+        const long long idx = first + (round * 4 + i) * 32 + lane;
+        uint4 odg, odu;
+        gate_grad_vec<T>(vd[i], vg[i], vu[i], odg, odu);
+        dg4[idx] = odg;
+        du4[idx] = odu;
+      }
+    }
+  }
+  __threadfence();
+  __syncwarp();
+  if (lane == 0) atomicAdd(p.ew_ctrl + 2 + v, 1u);
+}
+
 // ------------------------------------------------------------------ kernel --
 template <int MODE, int CG, int NSUB, typename T, bool ACC16>
 __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
@@ -784,7 +887,7 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
     ptx::prefetch_tensormap(&p.a0);
     ptx::prefetch_tensormap(&p.b0);
     ptx::prefetch_tensormap(&p.b1);
-    if (MODE == MODE_DX) ptx::prefetch_tensormap(&p.a1);
+    if (is_dx(MODE)) ptx::prefetch_tensormap(&p.a1);
     if (is_fwd(MODE)) {
       ptx::prefetch_tensormap(&p.sg);
       ptx::prefetch_tensormap(&p.su);
@@ -819,12 +922,41 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
       const uint64_t pol_b = ptx::make_l2_policy(p.l2_b);
       Pacer pacer{p.pace, p.pace_kb, p.pace_limit_ns, p.pace != nullptr && p.pace_kb > 0, 0};
       const int kb_per_tile = C::NSEG * num_kb;
+      int ew_ready_tile = -1;  // MODE_DXE: row tile whose gate gradient is known to be complete
       const unsigned int meets_per_tile =
           pacer.on ? static_cast<unsigned int>((kb_per_tile + pacer.kb - 1) / pacer.kb) : 0u;
       WorkItem w;
       for (int idx = 0; ok && next_work(p, kb_per_tile, cluster_id, num_clusters, idx, w); ++idx) {
         const int m0 = w.m_tile * C::TILE_M + cta_rank * C::BM;
         const int n0 = w.n_tile * C::TILE_N;
+        if (MODE == MODE_DXE && w.m_tile != ew_ready_tile) {
+          // dg / du rows of this row tile are produced by the epilogue warps of all CTAs
+          int v = w.m_tile - p.m_rotate;
+          if (v < 0) v += p.num_m_tiles;
+          const unsigned int* cnt = p.ew_ctrl + 2 + v;
+          atomicMax(p.ew_ctrl + 1, static_cast<unsigned int>(v) + 1u);  // how far the tiles have got
+          const uint64_t t0 = ptx::globaltimer_ns();
+          for (;;) {
+            unsigned int c;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(c) : "l"(cnt) : "memory");
+            if (c >= static_cast<unsigned int>(p.ew_qpm)) break;
+            if (*ctl.flag != 0u) {
+              ok = false;
+              break;
+            }
+            if (ptx::globaltimer_ns() - t0 > ctl.limit_ns) {
+              *ctl.flag = WAIT_GATE_GRAD_ROWS;
+              atomicCAS(ctl.status, 0u, WAIT_GATE_GRAD_ROWS | (static_cast<uint32_t>(blockIdx.x) << 8));
+              ok = false;
+              break;
+            }
+            __nanosleep(100);
+          }
+          if (!ok) break;
+          // the rows were written through the generic proxy; TMA reads them through the async proxy
+          asm volatile("fence.proxy.async;" ::: "memory");
+          ew_ready_tile = w.m_tile;
+        }
         // Whole tiles run in waves of num_clusters; every wave before the last is full,
         // and with a split tail every whole-tile wave is.
         const bool pace_item = pacer.on && w.slot < 0;
@@ -869,7 +1001,7 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
             if (C::A_BY_WARPS) {
               // written by the epilogue warps (see the transform loop below)
             } else if (C::A_MAJOR == MAJOR_K) {
-              load_a(a_dst, (MODE == MODE_DX && seg == 1) ? &p.a1 : &p.a0, k0, m0);
+              load_a(a_dst, (is_dx(MODE) && seg == 1) ? &p.a1 : &p.a0, k0, m0);
             } else {
 #pragma unroll
               for (int c = 0; c < C::BM / 64; ++c)
@@ -994,6 +1126,10 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
     bool ok = true;
     int xs = 0;        // A_BY_WARPS: stage and phase of the next A tile the warps write
     uint32_t xph = 0;
+    bool ew_more = (MODE == MODE_DXE);  // MODE_DXE: quanta of the side job may be left
+    const unsigned int ew_total = (MODE == MODE_DXE)
+                                      ? static_cast<unsigned int>(p.num_m_tiles) * static_cast<unsigned int>(p.ew_qpm)
+                                      : 0u;
     long long prof_wait = 0, prof_drain = 0, prof_t0 = 0, prof_tiles = 0;
     WorkItem w;
     for (int idx = 0; ok && next_work(p, C::NSEG * num_kb, cluster_id, num_clusters, idx, w); ++idx) {
@@ -1046,6 +1182,32 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
           }
         }
         if (!ok) break;
+      }
+      if (MODE == MODE_DXE) {
+        // Until this item's accumulators are complete, take quanta of the gate-gradient step.
+        while (ew_more) {
+          const uint32_t ready = ptx::mbar_try_wait(tfull_bar(NSUB == 2 ? 0 : a), aph) ? 1u : 0u;
+          if (__shfl_sync(0xffffffffu, ready, 0) != 0u) break;
+          unsigned int qn = 0xFFFFFFFFu;
+          if (lane == 0) {
+            const volatile unsigned int* c = p.ew_ctrl;
+            const unsigned int limit = (c[1] + static_cast<unsigned int>(p.ew_ahead)) * static_cast<unsigned int>(p.ew_qpm);
+            if (c[0] >= ew_total)
+              qn = ew_total;                       // nothing left
+            else if (c[0] < limit)
+              qn = atomicAdd(p.ew_ctrl, 1u);       // may overshoot the limit by a few quanta: harmless
+          }
+          qn = __shfl_sync(0xffffffffu, qn, 0);
+          if (qn == 0xFFFFFFFFu) {                 // far enough ahead for now
+            __nanosleep(500);
+            continue;
+          }
+          if (qn >= ew_total) {
+            ew_more = false;
+            break;
+          }
+          gate_grad_quantum<T, C::TILE_M>(p, qn, lane);
+        }
       }
       if (FSW_PROFILE) prof_t0 = clock64();
       ok = bounded_wait_warp(tfull_bar(NSUB == 2 ? 0 : a), aph, ctl, WAIT_EPI_TMEM_FULL);
@@ -1100,6 +1262,18 @@ __global__ void __launch_bounds__(64 + 32 * FSW_EPI_WARPS, 1)
       } else {
         a ^= 1;
         if (a == 0) aph ^= 1u;
+      }
+    }
+    if (MODE == MODE_DXE) {
+      // a CTA pair with few or no tiles still helps until the queue is empty
+      while (ew_more && ok) {
+        unsigned int qn = 0;
+        if (lane == 0) qn = atomicAdd(p.ew_ctrl, 1u);
+        qn = __shfl_sync(0xffffffffu, qn, 0);
+        if (qn >= ew_total)
+          ew_more = false;
+        else
+          gate_grad_quantum<T, C::TILE_M>(p, qn, lane);
       }
     }
     if (is_fwd(MODE)) {

@@ -158,6 +158,20 @@ int fsw_backward_elementwise_st(const void* dout, const void* s, const void* t, 
                                 int64_t numel, int dtype, void* stream);
 
 /*
+ * fsw_backward_elementwise and fsw_backward_dx_ws as ONE launch (replaces
+ * kernels_bf16.py:210-255 + swiglu.py:45): the dX GEMM's epilogue warps, idle while a
+ * tile's K loop runs, compute dg and du (same arithmetic and rounding points as
+ * fsw_backward_elementwise, once per element) ahead of the tiles that read them; a tile's
+ * loads wait - time-limited - until the rows they need are complete.  dg and du (T, di)
+ * are outputs here, for fsw_backward_dw.  Results are bit-identical to the two separate
+ * calls.  Falls back to them when the launch would not use 256-row tiles of SM pairs or
+ * T exceeds 2 Mi rows, or with option "gate_in_dx" = 0.
+ */
+int fsw_backward_dx_gate(const void* dout, const void* g, const void* u, const void* w_gate,
+                         const void* w_up, void* dx, void* dg, void* du, int64_t T, int64_t dm,
+                         int64_t di, void* workspace, int64_t workspace_bytes, int dtype, void* stream);
+
+/*
  * dX reduced across GPUs inside the kernels (no counterpart in the reference, which
  * is single-GPU).  With d_intermediate split over `world` ranks (2..8) every rank's
  * dX GEMM yields a partial sum of the whole (T, dm) gradient.  Rank r owns rows

@@ -419,6 +419,30 @@ def test_gate_gradient_inside_the_dx_gemm(T, dm, di, dtype):
         assert e < (4e-3 if dtype == "bf16" else 6e-4), (name, e)
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("T,dm,di", [(1000, 320, 1096), (4224, 512, 2304), (8200, 4096, 1536), (300, 64, 8)])
+def test_gate_gradient_step_as_a_side_job_of_the_dx_kernel(T, dm, di, dtype):
+    """fsw_backward_dx_gate: the elementwise step runs on the dX kernel's idle epilogue
+    warps, in 2048-element quanta ahead of the tiles whose loads wait for their rows.  Same
+    arithmetic, so dg, du and dX must be bit-identical to the two separate launches; six
+    launches in a row go round the ring of control slots.  Ragged T (a partial last row
+    tile), d_intermediate that is not a multiple of 64, several waves of tiles."""
+    from fusedswiglu_b200 import _launch, _lib
+
+    inp = orc.make_inputs(1, T, dm, di, dtype, seed=T + dm, dout_std=0.5)
+    x, wg, wu = dev(inp["x"].reshape(T, dm), dtype), dev(inp["w_gate"], dtype), dev(inp["w_up"], dtype)
+    dout = dev(inp["dout"].reshape(T, di), dtype)
+    _, g, u = _launch.forward(x, wg, wu)
+    dg0, du0 = _launch.gate_grad(dout, g, u)
+    dx0 = _launch.grad_input(dg0, du0, wg, wu)
+    for _ in range(6):
+        dx, dg, du = _launch.gate_grad_and_input(dout, g, u, wg, wu)
+        torch.cuda.synchronize()
+        assert torch.equal(dg, dg0) and torch.equal(du, du0)
+        assert torch.equal(dx, dx0)
+    assert _lib.device_status() == 0
+
+
 def test_fused_gate_gradient_mode_of_the_autograd_function():
     """FusedSwiGLU.fused_gate_grad = True on shapes of the reference's backward test,
     with its tolerance, against the PyTorch SwiGLU + autograd."""
