@@ -66,3 +66,51 @@ def test_product_does_not_import_the_oracle():
         text = p.read_text()
         for needle in ("import oracle", "from oracle", "swiglu_oracle", "oracle/", "oracle."):
             assert needle not in text, f"{p} refers to the oracle package ({needle!r})"
+
+
+def test_bench_parity_report_on_cpu_tensors():
+    """The bench's per-tensor parity reporter, fed from the CPU: exact float64 results give
+    errors at the level of one bf16 rounding, a corrupted tensor is flagged above the bound."""
+    import torch
+
+    import bench
+
+    torch.manual_seed(0)
+    T, dm, di = 192, 64, 96
+    x = torch.randn(T, dm).bfloat16()
+    wg, wu = (torch.randn(dm, di) / dm ** 0.5).bfloat16(), (torch.randn(dm, di) / dm ** 0.5).bfloat16()
+    dout = torch.randn(T, di).bfloat16()
+    g, u = x.double() @ wg.double(), x.double() @ wu.double()
+    s = torch.sigmoid(g)
+    out = torch.nn.functional.silu(g) * u
+    dg, du = dout.double() * u * (s + g * s * (1 - s)), dout.double() * g * s
+    dx = dg @ wg.double().T + du @ wu.double().T
+    dwg, dwu = x.double().T @ dg, x.double().T @ du
+    good = [t.bfloat16() for t in (out, dx, dwg, dwu)]
+    rep = bench.parity_report(x, wg, wu, dout, *good, world=1)
+    assert rep["ok"] and all(rep[k]["rel_fro"] < 4e-3 for k in ("out", "dx", "dw_gate", "dw_up")), rep
+    assert all(rep[k]["max_abs"] >= 0 and rep[k]["max_rel"] >= 0 for k in ("out", "dx", "dw_gate", "dw_up"))
+    bad = list(good)
+    bad[1] = (dx * 1.05).bfloat16()  # 5 % off: far above the 1e-2 bound
+    rep = bench.parity_report(x, wg, wu, dout, *bad, world=1)
+    assert not rep["ok"] and rep["dx"]["rel_fro"] > 1e-2 and rep["out"]["rel_fro"] < 4e-3
+
+
+def test_bench_cpu_sample_rule_and_sampler_without_a_gpu():
+    import time
+
+    import bench
+
+    # the whole 8B workload fits the CPU budget, the 70B one is cut to T/8
+    assert bench.cpu_sample_tokens(32768, 4096, 14336) == 32768
+    assert bench.cpu_sample_tokens(65536, 8192, 28672) == 8192
+    assert bench.flops_per_step(32768, 4096, 14336) == 12.0 * 32768 * 4096 * 14336
+    assert bench.host_threads() >= 1
+    # without NVML / nvidia-smi the sampler yields an empty record instead of failing
+    s = bench.ClockSampler("GPU-00000000-0000-0000-0000-000000000000", 0)
+    t0 = time.time()
+    s.start()
+    rec = s.summary(t0, time.time() + 1, "test")
+    assert rec["samples"] >= 0 and "reasons" in rec
+    assert bench.load_dram_traffic("fwd_dual_gemm", "llama3_8b_mlp", 1) > 1e9
+    assert bench.load_dram_traffic("fwd_dual_gemm", "llama3_8b_mlp", 8) is None
